@@ -1,0 +1,170 @@
+/*
+ * msd_b200 — C ABI of the B200-native Mixed-Scale Dense (MSD) convolution library.
+ *
+ * Every entry point replaces one function of the reference's native module
+ * `msd_custom_convolutions` (ahendriksen/msd_pytorch,
+ * msd_pytorch/msd_custom_convolutions.cpp:343-369, launchers declared in
+ * msd_pytorch/msd_custom_convolutions/torch_cuda_dispatch.h:4-49) or the Python
+ * loop of `MSDBlockFunction` above it (msd_pytorch/msd_block.py:8-134).
+ *
+ * Conventions
+ *  - All pointers are DEVICE pointers owned by the caller; nothing is retained.
+ *  - Data tensors are described by `msd_tensor_t`: dimensions in the order
+ *    N, C, [Z,] Y, X (ndim 4 = 2D images, ndim 5 = 3D volumes), sizes and
+ *    strides in ELEMENTS.  Arbitrary strides are honoured (channel-slice views
+ *    of one dense buffer are the normal case).  Convolution weights are dense
+ *    `[c_out, c_in, 3, 3(, 3)]`; bias is dense `[c_out]`.
+ *  - `dtype` is MSD_F32 or MSD_F64 for every tensor of a call.
+ *  - Work is enqueued asynchronously on `stream` (a `cudaStream_t`) of CUDA
+ *    device ordinal `device`; the library switches to that device for the call
+ *    and restores the previous one.
+ *  - Padding is the reference's edge-inclusive reflection: index -k reads k-1,
+ *    index n-1+k reads n-k (msd_custom_convolutions/kernel_utils.cuh:30-38);
+ *    it requires 1 <= dilation <= every spatial size.
+ *  - `grad_input`, `grad_kernel`, `grad_bias` are ACCUMULATED INTO, like the
+ *    reference (conv2d_backward_x.cu:103, conv2d_backward_k.cu:52,
+ *    conv2d_backward_bias.cu:46); `output` is overwritten.
+ *  - Weight and bias gradients are deterministic: per-block partial sums are
+ *    written to `workspace` and added in a fixed order by a second kernel.
+ *    `workspace` must hold `msd_workspace_bytes()` bytes, be 256-byte aligned
+ *    and not be shared by calls that may overlap on the GPU.
+ *  - Return value: MSD_OK or an error code; `msd_last_error_string()` gives the
+ *    message of the calling thread's last failure.  Nothing throws.
+ *  - Thread-safe and re-entrant (the only global state is a mutex-protected
+ *    cache of TMA descriptors and launch configurations).
+ */
+#ifndef MSD_B200_H
+#define MSD_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define MSD_API __attribute__((visibility("default")))
+#else
+#define MSD_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MSD_OK 0
+#define MSD_ERR_BAD_ARGUMENT 1 /* shapes / ranks / dilation do not satisfy the op's contract */
+#define MSD_ERR_UNSUPPORTED 2  /* dtype or size outside what the library implements */
+#define MSD_ERR_WORKSPACE 3    /* workspace missing, misaligned or too small */
+#define MSD_ERR_CUDA 4         /* a CUDA runtime / driver call or a launch failed */
+#define MSD_ERR_LIMIT 5        /* size beyond a stated fixed maximum (no-allocation entry point) */
+
+#define MSD_F32 0
+#define MSD_F64 1
+
+#define MSD_MAX_DIMS 5
+
+typedef struct msd_tensor {
+    void *data;
+    int32_t ndim; /* 4 (N,C,Y,X) or 5 (N,C,Z,Y,X) */
+    int32_t reserved;
+    int64_t size[MSD_MAX_DIMS];
+    int64_t stride[MSD_MAX_DIMS]; /* in elements */
+} msd_tensor_t;
+
+/* Library version (major*10000 + minor*100 + patch). */
+MSD_API int msd_version(void);
+
+/* Message of the calling thread's most recent error ("" if none). */
+MSD_API const char *msd_last_error_string(void);
+
+/* Upper bound, in bytes, of the scratch `workspace` any backward entry point
+ * below needs for these sizes (`voxels` = N * prod(spatial)). */
+MSD_API size_t msd_workspace_bytes(int dtype, int ndim, int64_t voxels, int64_t c_in, int64_t c_out);
+
+/* ---- single operations: the eight functions of `msd_custom_convolutions` ---- */
+
+/* conv_forward (msd_custom_convolutions.cpp:85-116; conv2d_forward.cu:22-93, conv3d_forward.cu:22-108) */
+MSD_API int msd_conv_forward(int dtype, const msd_tensor_t *input, const void *kernel, const void *bias,
+                     const msd_tensor_t *output, int dilation, int device, void *stream);
+
+/* conv_relu_forward (msd_custom_convolutions.cpp:213-245; conv2d_forward.cu:95-174, conv3d_forward.cu:110-196) */
+MSD_API int msd_conv_relu_forward(int dtype, const msd_tensor_t *input, const void *kernel, const void *bias,
+                          const msd_tensor_t *output, int dilation, int device, void *stream);
+
+/* conv_backward_x (msd_custom_convolutions.cpp:118-148; conv2d_backward_x.cu:13-106, conv3d_backward_x.cu:13-123) */
+MSD_API int msd_conv_backward_x(int dtype, const msd_tensor_t *grad_output, const void *kernel,
+                        const msd_tensor_t *grad_input, int dilation, int device, void *stream);
+
+/* conv_relu_backward_x (msd_custom_convolutions.cpp:247-281; conv2d_backward_x.cu:109-208, conv3d_backward_x.cu:125-241) */
+MSD_API int msd_conv_relu_backward_x(int dtype, const msd_tensor_t *output, const msd_tensor_t *grad_output,
+                             const void *kernel, const msd_tensor_t *grad_input, int dilation,
+                             int device, void *stream);
+
+/* conv_backward_k (msd_custom_convolutions.cpp:150-178; conv2d_backward_k.cu:12-59, conv3d_backward_k.cu:11-64) */
+MSD_API int msd_conv_backward_k(int dtype, const msd_tensor_t *grad_output, const msd_tensor_t *input,
+                        void *grad_kernel, int dilation, void *workspace, size_t workspace_bytes,
+                        int device, void *stream);
+
+/* conv_relu_backward_k (msd_custom_convolutions.cpp:283-316; conv2d_backward_k.cu:61-112, conv3d_backward_k.cu:66-122) */
+MSD_API int msd_conv_relu_backward_k(int dtype, const msd_tensor_t *output, const msd_tensor_t *grad_output,
+                             const msd_tensor_t *input, void *grad_kernel, int dilation,
+                             void *workspace, size_t workspace_bytes, int device, void *stream);
+
+/* conv_backward_bias (msd_custom_convolutions.cpp:180-211, an ATen sum in the reference) */
+MSD_API int msd_conv_backward_bias(int dtype, const msd_tensor_t *grad_output, void *grad_bias,
+                           void *workspace, size_t workspace_bytes, int device, void *stream);
+
+/* conv_relu_backward_bias (msd_custom_convolutions.cpp:318-338; conv2d_backward_bias.cu:12-49, conv3d_backward_bias.cu:12-51) */
+MSD_API int msd_conv_relu_backward_bias(int dtype, const msd_tensor_t *output, const msd_tensor_t *grad_output,
+                                void *grad_bias, void *workspace, size_t workspace_bytes,
+                                int device, void *stream);
+
+/* ---- whole dense block: the loops of MSDBlockFunction (msd_block.py:8-134) ---- */
+
+/* Forward of all `depth` layers over ONE buffer `result[N, c_in + depth*width, ...]`
+ * whose first `c_in` channels already hold the input (msd_block.py:30-58).
+ * Layer i reads channels [0, c_in + i*width) and writes the next `width` channels:
+ * ReLU(conv_{dilations[i]} + bias).  `weights` is a HOST array of `depth` device
+ * pointers, weights[i] dense [width, c_in + i*width, 3, 3(, 3)]; `bias` is a device
+ * pointer to depth*width values; `dilations` is a HOST array. */
+MSD_API int msd_block_forward(int dtype, const msd_tensor_t *result, int c_in, int depth, int width,
+                      const void *const *weights, const void *bias, const int *dilations,
+                      int device, void *stream);
+
+/* Backward of all layers, last to first (msd_block.py:64-134).  `gradients` has the
+ * shape of `result` and holds the gradient w.r.t. every channel on entry; it is
+ * updated in place and its first `c_in` channels are the input gradient on return.
+ * Higher channels are left in a library-defined state.
+ * `grad_weights` is a HOST array of `depth` device pointers (an entry may be NULL to
+ * skip that layer's weight gradient); `grad_bias` may be NULL.  Both are accumulated
+ * into. */
+MSD_API int msd_block_backward(int dtype, const msd_tensor_t *result, const msd_tensor_t *gradients,
+                       int c_in, int depth, int width, const void *const *weights,
+                       const int *dilations, void *const *grad_weights, void *grad_bias,
+                       void *workspace, size_t workspace_bytes, int device, void *stream);
+
+/* Scratch bytes `msd_block_backward` needs. */
+MSD_API size_t msd_block_workspace_bytes(int dtype, int ndim, int64_t voxels, int c_in, int depth, int width);
+
+/* ---- launch autotuner (replaces benchmarks/benchmark_block_sizes.py) ---- */
+
+/* Number of launch variants the library has for a kernel family
+ * (family: 0 = 2D forward, 1 = 2D backward, 2 = 3D forward, 3 = 3D backward). */
+MSD_API int msd_tuning_num_variants(int family);
+
+/* Force variant `variant` (or -1 = library default) for (family, dilation).
+ * Used by the Python autotuner, which times the variants on the caller's shapes
+ * and stores the winners on disk. */
+MSD_API int msd_tuning_set(int family, int dilation, int variant);
+MSD_API int msd_tuning_get(int family, int dilation);
+
+/* Counters for tests and benchmarks: number of kernels this library launched in
+ * the calling process since load / since the last reset, and how many of those
+ * took the tuned sm_100a path (TMA-staged forward, register-resident fused
+ * backward) rather than the generic one. */
+MSD_API int64_t msd_launch_count(void);
+MSD_API int64_t msd_fast_launch_count(void);
+MSD_API void msd_reset_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MSD_B200_H */

@@ -1,0 +1,6 @@
+"""3D convolution ops and modules (API of the reference's msd_pytorch/conv3d.py)."""
+from ._convnd import make_namespace
+
+_ns = make_namespace(3)
+globals().update(_ns)
+__all__ = sorted(_ns)

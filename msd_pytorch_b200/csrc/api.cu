@@ -1,0 +1,296 @@
+// extern "C" entry points of libmsd_b200: argument validation and dispatch between the
+// tuned sm_100a kernels (float32, one output channel) and the generic kernels.
+#include <atomic>
+#include <string.h>
+#include "common.cuh"
+#include "kernels.h"
+
+namespace msd {
+
+thread_local char g_error[512] = "";
+
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+static std::atomic<int64_t> g_launches{0}, g_fast_launches{0};
+void count_launch(bool fast) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (fast) g_fast_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+static bool same_geometry(const View &a, const View &b) { return a.n == b.n && a.z == b.z && a.y == b.y && a.x == b.x; }
+
+static int check_dtype(int dtype) {
+    if (dtype != MSD_F32 && dtype != MSD_F64) MSD_FAIL(MSD_ERR_UNSUPPORTED, "dtype %d is not MSD_F32 or MSD_F64", dtype);
+    return MSD_OK;
+}
+
+// Mirrors checkDilation (msd_custom_convolutions.cpp:39-52).
+static int check_dilation(const char *op, const View &v, int nd, int d) {
+    if (d <= 0) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: Dilation must be 1 or greater", op);
+    if (d > v.y || d > v.x || (nd == 3 && d > v.z)) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: Dilation cannot be greater than size of image.", op);
+    return MSD_OK;
+}
+
+// Mirrors checkInOutShape (msd_custom_convolutions.cpp:69-83).
+static int views2(const char *op, const msd_tensor_t *a, const msd_tensor_t *b, View *va, View *vb, int *nd) {
+    if (!make_view(a, va) || !make_view(b, vb)) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: tensors must be 4- or 5-dimensional and non-null", op);
+    if (a->ndim != b->ndim) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: tensors differ in number of dimensions", op);
+    if (va->n != vb->n) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: Input batch dimension does not match output batch dimension.", op);
+    if (!same_geometry(*va, *vb)) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: Input shape does not match output shape.", op);
+    *nd = a->ndim - 2;
+    return MSD_OK;
+}
+
+static int forward_impl(const char *op, bool relu, int dtype, const msd_tensor_t *input, const void *kernel, const void *bias,
+                        const msd_tensor_t *output, int d, int device, void *stream) {
+    int rc = check_dtype(dtype);
+    if (rc) return rc;
+    View in, out;
+    int nd;
+    if ((rc = views2(op, input, output, &in, &out, &nd))) return rc;
+    if (!kernel || !bias) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: kernel and bias must not be null", op);
+    if ((rc = check_dilation(op, in, nd, d))) return rc;
+    DeviceGuard g(device);
+    MSD_CUDA_TRY(g.status);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == MSD_F32 && out.c == 1 && fast::forward_supported(in, out, nd, d))
+        return fast::forward(relu, in, (const float *)kernel, (const float *)bias, out, nd, d, device, s);
+    return generic::forward(dtype, relu, in, kernel, bias, out, nd, d, s);
+}
+
+static int backward_x_impl(const char *op, bool relu, int dtype, const msd_tensor_t *output, const msd_tensor_t *grad_output, const void *kernel,
+                           const msd_tensor_t *grad_input, int d, int device, void *stream) {
+    int rc = check_dtype(dtype);
+    if (rc) return rc;
+    View out, gout, gin;
+    int nd;
+    if ((rc = views2(op, grad_output, grad_input, &gout, &gin, &nd))) return rc;
+    if (relu) {
+        int nd2;
+        if ((rc = views2(op, output, grad_output, &out, &gout, &nd2))) return rc;
+        if (out.c != gout.c) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: output and grad_output differ in channels", op);
+    }
+    if (!kernel) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: kernel must not be null", op);
+    if ((rc = check_dilation(op, gout, nd, d))) return rc;
+    DeviceGuard g(device);
+    MSD_CUDA_TRY(g.status);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == MSD_F32 && gout.c == 1) {
+        fast::BackwardArgs a{relu ? &out : nullptr, &gout, nullptr, &gin, (const float *)kernel, nullptr, nullptr, nd, d, nullptr, 0};
+        if (fast::backward_supported(a)) return fast::backward(a, device, s);
+    }
+    return generic::backward_x(dtype, relu, relu ? &out : nullptr, gout, kernel, gin, nd, d, s);
+}
+
+static int backward_k_impl(const char *op, bool relu, int dtype, const msd_tensor_t *output, const msd_tensor_t *grad_output,
+                           const msd_tensor_t *input, void *grad_kernel, int d, void *ws, size_t wsb, int device, void *stream) {
+    int rc = check_dtype(dtype);
+    if (rc) return rc;
+    View out, gout, in;
+    int nd;
+    if ((rc = views2(op, input, grad_output, &in, &gout, &nd))) return rc;
+    if (relu) {
+        int nd2;
+        if ((rc = views2(op, output, grad_output, &out, &gout, &nd2))) return rc;
+        if (out.c != gout.c) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: output and grad_output differ in channels", op);
+    }
+    if (!grad_kernel) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: grad_kernel must not be null", op);
+    if ((rc = check_dilation(op, in, nd, d))) return rc;
+    if (ws && ((uintptr_t)ws & 255)) MSD_FAIL(MSD_ERR_WORKSPACE, "%s: workspace must be 256-byte aligned", op);
+    DeviceGuard g(device);
+    MSD_CUDA_TRY(g.status);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == MSD_F32 && gout.c == 1) {
+        fast::BackwardArgs a{relu ? &out : nullptr, &gout, &in, nullptr, nullptr, (float *)grad_kernel, nullptr, nd, d, ws, wsb};
+        if (fast::backward_supported(a)) return fast::backward(a, device, s);
+    }
+    return generic::backward_k(dtype, relu, relu ? &out : nullptr, gout, in, grad_kernel, nd, d, ws, wsb, s);
+}
+
+static int backward_bias_impl(const char *op, bool relu, int dtype, const msd_tensor_t *output, const msd_tensor_t *grad_output, void *grad_bias,
+                              void *ws, size_t wsb, int device, void *stream) {
+    int rc = check_dtype(dtype);
+    if (rc) return rc;
+    View out, gout;
+    if (!make_view(grad_output, &gout)) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: grad_output must be 4- or 5-dimensional and non-null", op);
+    if (relu) {
+        int nd2;
+        if ((rc = views2(op, output, grad_output, &out, &gout, &nd2))) return rc;
+        if (out.c != gout.c) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: output and grad_output differ in channels", op);
+    }
+    if (!grad_bias) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: grad_bias must not be null", op);
+    if (ws && ((uintptr_t)ws & 255)) MSD_FAIL(MSD_ERR_WORKSPACE, "%s: workspace must be 256-byte aligned", op);
+    DeviceGuard g(device);
+    MSD_CUDA_TRY(g.status);
+    return generic::backward_bias(dtype, relu, relu ? &out : nullptr, gout, grad_bias, ws, wsb, (cudaStream_t)stream);
+}
+
+static View channel_slice(const View &v, int64_t c0, int64_t nc, size_t elem) {
+    View s = v;
+    s.p = (char *)v.p + c0 * v.sc * (int64_t)elem;
+    s.c = nc;
+    return s;
+}
+
+}  // namespace msd
+
+using namespace msd;
+
+extern "C" {
+
+int msd_version(void) { return 100; }
+
+const char *msd_last_error_string(void) { return g_error; }
+
+size_t msd_workspace_bytes(int dtype, int ndim, int64_t voxels, int64_t c_in, int64_t c_out) {
+    const int nd = ndim == 5 ? 3 : 2;
+    size_t a = generic::workspace_bytes(dtype, nd, voxels, c_in, c_out);
+    size_t b = fast::backward_workspace_bytes(nd, c_in);
+    return a > b ? a : b;
+}
+
+int msd_conv_forward(int dtype, const msd_tensor_t *input, const void *kernel, const void *bias, const msd_tensor_t *output, int dilation,
+                     int device, void *stream) {
+    return forward_impl("conv_forward", false, dtype, input, kernel, bias, output, dilation, device, stream);
+}
+
+int msd_conv_relu_forward(int dtype, const msd_tensor_t *input, const void *kernel, const void *bias, const msd_tensor_t *output, int dilation,
+                          int device, void *stream) {
+    return forward_impl("conv_relu_forward", true, dtype, input, kernel, bias, output, dilation, device, stream);
+}
+
+int msd_conv_backward_x(int dtype, const msd_tensor_t *grad_output, const void *kernel, const msd_tensor_t *grad_input, int dilation, int device,
+                        void *stream) {
+    return backward_x_impl("conv_backward_x", false, dtype, nullptr, grad_output, kernel, grad_input, dilation, device, stream);
+}
+
+int msd_conv_relu_backward_x(int dtype, const msd_tensor_t *output, const msd_tensor_t *grad_output, const void *kernel,
+                             const msd_tensor_t *grad_input, int dilation, int device, void *stream) {
+    return backward_x_impl("conv_relu_backward_x", true, dtype, output, grad_output, kernel, grad_input, dilation, device, stream);
+}
+
+int msd_conv_backward_k(int dtype, const msd_tensor_t *grad_output, const msd_tensor_t *input, void *grad_kernel, int dilation, void *workspace,
+                        size_t workspace_bytes, int device, void *stream) {
+    return backward_k_impl("conv_backward_k", false, dtype, nullptr, grad_output, input, grad_kernel, dilation, workspace, workspace_bytes, device,
+                           stream);
+}
+
+int msd_conv_relu_backward_k(int dtype, const msd_tensor_t *output, const msd_tensor_t *grad_output, const msd_tensor_t *input, void *grad_kernel,
+                             int dilation, void *workspace, size_t workspace_bytes, int device, void *stream) {
+    return backward_k_impl("conv_relu_backward_k", true, dtype, output, grad_output, input, grad_kernel, dilation, workspace, workspace_bytes,
+                           device, stream);
+}
+
+int msd_conv_backward_bias(int dtype, const msd_tensor_t *grad_output, void *grad_bias, void *workspace, size_t workspace_bytes, int device,
+                           void *stream) {
+    return backward_bias_impl("conv_backward_bias", false, dtype, nullptr, grad_output, grad_bias, workspace, workspace_bytes, device, stream);
+}
+
+int msd_conv_relu_backward_bias(int dtype, const msd_tensor_t *output, const msd_tensor_t *grad_output, void *grad_bias, void *workspace,
+                                size_t workspace_bytes, int device, void *stream) {
+    return backward_bias_impl("conv_relu_backward_bias", true, dtype, output, grad_output, grad_bias, workspace, workspace_bytes, device, stream);
+}
+
+static int block_checks(const char *op, int dtype, const msd_tensor_t *result, int c_in, int depth, int width, const void *const *weights,
+                        const int *dilations, View *r, int *nd) {
+    int rc = check_dtype(dtype);
+    if (rc) return rc;
+    if (!make_view(result, r)) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: buffer must be 4- or 5-dimensional and non-null", op);
+    *nd = result->ndim - 2;
+    if (c_in < 1 || depth < 1 || width < 1) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: c_in, depth and width must be at least 1", op);
+    if (r->c != (int64_t)c_in + (int64_t)depth * width)
+        MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: buffer has %lld channels, expected c_in + depth*width = %lld", op, (long long)r->c,
+                 (long long)c_in + (long long)depth * width);
+    if (!weights || !dilations) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: weights and dilations must not be null", op);
+    for (int i = 0; i < depth; ++i) {
+        if (!weights[i]) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: weights[%d] is null", op, i);
+        if ((rc = check_dilation(op, *r, *nd, dilations[i]))) return rc;
+    }
+    return MSD_OK;
+}
+
+int msd_block_forward(int dtype, const msd_tensor_t *result, int c_in, int depth, int width, const void *const *weights, const void *bias,
+                      const int *dilations, int device, void *stream) {
+    View r;
+    int nd;
+    int rc = block_checks("msd_block_forward", dtype, result, c_in, depth, width, weights, dilations, &r, &nd);
+    if (rc) return rc;
+    if (!bias) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "msd_block_forward: bias must not be null");
+    DeviceGuard g(device);
+    MSD_CUDA_TRY(g.status);
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t es = dtype == MSD_F64 ? 8 : 4;
+    for (int i = 0; i < depth; ++i) {
+        const int64_t n_i = c_in + (int64_t)i * width;
+        View in = channel_slice(r, 0, n_i, es);
+        View out = channel_slice(r, n_i, width, es);
+        const void *b = (const char *)bias + (size_t)i * width * es;
+        const int d = dilations[i];
+        if (dtype == MSD_F32 && width == 1 && fast::forward_supported(in, out, nd, d))
+            rc = fast::forward(true, in, (const float *)weights[i], (const float *)b, out, nd, d, device, s);
+        else
+            rc = generic::forward(dtype, true, in, weights[i], b, out, nd, d, s);
+        if (rc) return rc;
+    }
+    return MSD_OK;
+}
+
+size_t msd_block_workspace_bytes(int dtype, int ndim, int64_t voxels, int c_in, int depth, int width) {
+    const int64_t n_max = c_in + (int64_t)(depth - 1) * width;
+    return msd_workspace_bytes(dtype, ndim, voxels, n_max, width);
+}
+
+int msd_block_backward(int dtype, const msd_tensor_t *result, const msd_tensor_t *gradients, int c_in, int depth, int width,
+                       const void *const *weights, const int *dilations, void *const *grad_weights, void *grad_bias, void *workspace,
+                       size_t workspace_bytes, int device, void *stream) {
+    View r, gr;
+    int nd, nd2;
+    int rc = block_checks("msd_block_backward", dtype, result, c_in, depth, width, weights, dilations, &r, &nd);
+    if (rc) return rc;
+    if ((rc = views2("msd_block_backward", result, gradients, &r, &gr, &nd2))) return rc;
+    if (gr.c != r.c) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "msd_block_backward: gradients and result differ in channels");
+    if (workspace && ((uintptr_t)workspace & 255)) MSD_FAIL(MSD_ERR_WORKSPACE, "msd_block_backward: workspace must be 256-byte aligned");
+    DeviceGuard g(device);
+    MSD_CUDA_TRY(g.status);
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t es = dtype == MSD_F64 ? 8 : 4;
+    for (int i = depth - 1; i >= 0; --i) {
+        const int64_t n_i = c_in + (int64_t)i * width;
+        View out = channel_slice(r, n_i, width, es);
+        View in = channel_slice(r, 0, n_i, es);
+        View gout = channel_slice(gr, n_i, width, es);
+        View gin = channel_slice(gr, 0, n_i, es);
+        const int d = dilations[i];
+        void *gk = grad_weights ? grad_weights[i] : nullptr;
+        void *gb = grad_bias ? (char *)grad_bias + (size_t)i * width * es : nullptr;
+        if (dtype == MSD_F32 && width == 1) {
+            fast::BackwardArgs a{&out, &gout, &in, &gin, (const float *)weights[i], (float *)gk, (float *)gb, nd, d, workspace, workspace_bytes};
+            if (fast::backward_supported(a)) {
+                if ((rc = fast::backward(a, device, s))) return rc;
+                continue;
+            }
+        }
+        if ((rc = generic::backward_x(dtype, true, &out, gout, weights[i], gin, nd, d, s))) return rc;
+        if (gk && (rc = generic::backward_k(dtype, true, &out, gout, in, gk, nd, d, workspace, workspace_bytes, s))) return rc;
+        if (gb && (rc = generic::backward_bias(dtype, true, &out, gout, gb, workspace, workspace_bytes, s))) return rc;
+    }
+    return MSD_OK;
+}
+
+int msd_tuning_num_variants(int family) { return fast::num_variants(family); }
+int msd_tuning_set(int family, int dilation, int variant) { return fast::tuning_set(family, dilation, variant); }
+int msd_tuning_get(int family, int dilation) { return fast::tuning_get(family, dilation); }
+
+int64_t msd_launch_count(void) { return g_launches.load(); }
+int64_t msd_fast_launch_count(void) { return g_fast_launches.load(); }
+void msd_reset_launch_count(void) {
+    g_launches.store(0);
+    g_fast_launches.store(0);
+}
+
+}  // extern "C"

@@ -1,0 +1,52 @@
+// Internal interfaces between the C ABI (api.cu) and the kernel files.
+#pragma once
+#include "common.cuh"
+
+namespace msd {
+
+namespace generic {
+size_t workspace_bytes(int dtype, int nd, int64_t nvox, int64_t c_in, int64_t c_out);
+int forward(int dtype, bool relu, const View &in, const void *k, const void *bias, const View &out, int nd, int d, cudaStream_t s);
+int backward_x(int dtype, bool relu, const View *out, const View &gout, const void *k, const View &gin, int nd, int d, cudaStream_t s);
+int backward_k(int dtype, bool relu, const View *out, const View &gout, const View &in, void *gk, int nd, int d, void *ws, size_t wsb,
+               cudaStream_t s);
+int backward_bias(int dtype, bool relu, const View *out, const View &gout, void *gb, void *ws, size_t wsb, cudaStream_t s);
+}  // namespace generic
+
+// Tuned float32 kernels for layers that emit ONE channel (the MSD block with
+// width 1).  Each `*_supported` predicate is checked by the dispatcher; when it
+// says no, the generic kernel runs instead.
+namespace fast {
+
+enum Family { FWD2D = 0, BWD2D = 1, FWD3D = 2, BWD3D = 3, NUM_FAMILIES = 4 };
+int num_variants(int family);
+int tuning_set(int family, int dilation, int variant);
+int tuning_get(int family, int dilation);
+
+// Forward: out = [relu](bias + conv_d(in)), in has C channels, out has 1.
+bool forward_supported(const View &in, const View &out, int nd, int d);
+int forward(bool relu, const View &in, const float *k, const float *bias, const View &out, int nd, int d, int device, cudaStream_t s);
+
+// Fused backward of one layer.  m = gout * gate(out); for every input channel c:
+//   gin[c] += conv_d^T(m, k[c])        (if gin)
+//   gk[c,:] += <in[c] shifted, m>      (if gk; deterministic two-pass)
+//   gb      += sum m                   (if gb)
+// `out` may be null (no gate).  `in` may be null when gk is null.
+struct BackwardArgs {
+    const View *out;   // [N,1,...] ReLU output (gate) or null
+    const View *gout;  // [N,1,...]
+    const View *in;    // [N,C,...] or null
+    const View *gin;   // [N,C,...] or null
+    const float *k;    // [1,C,taps] or null (needed when gin)
+    float *gk;         // [1,C,taps] accumulated, or null
+    float *gb;         // [1] accumulated, or null
+    int nd, d;
+    void *ws;
+    size_t wsb;
+};
+bool backward_supported(const BackwardArgs &a);
+size_t backward_workspace_bytes(int nd, int64_t c_in);
+int backward(const BackwardArgs &a, int device, cudaStream_t s);
+
+}  // namespace fast
+}  // namespace msd

@@ -1,0 +1,88 @@
+"""CPU tests of the C-ABI boundary: the library loads, exports every symbol that
+include/msd_b200.h declares, and rejects bad arguments before touching a GPU."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "msd_b200.h")).read()
+    return sorted(set(re.findall(r"MSD_API[^;(]*?\b(msd_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from msd_pytorch_b200 import _lib
+
+    names = declared_symbols()
+    assert len(names) >= 20
+    raw = ctypes.CDLL(_lib.LIB_PATH)
+    for n in names:
+        assert hasattr(raw, n), "libmsd_b200.so does not export " + n
+    assert set(names) == set(_lib.EXPORTED), "binding and header disagree"
+    assert _lib.lib.msd_version() >= 100
+
+
+def test_package_has_no_fallback(monkeypatch):
+    """Without the shared library the package refuses to import."""
+    from msd_pytorch_b200 import _lib
+
+    monkeypatch.setattr(_lib, "LIB_PATH", os.path.join(ROOT, "does_not_exist.so"))
+    with pytest.raises(ImportError):
+        _lib._load()
+
+
+def test_cpu_tensors_are_rejected():
+    # msd_custom_convolutions.cpp:98: every op rejects CPU tensors.
+    from msd_pytorch_b200 import msd_custom_convolutions as cc
+
+    x = torch.zeros(1, 1, 4, 4)
+    with pytest.raises(RuntimeError):
+        cc.conv_forward(x, torch.zeros(1, 1, 3, 3), torch.zeros(1), torch.zeros(1, 1, 4, 4), 1, block_size=(0, 16, 16))
+
+
+def _desc(shape, strides=None, ptr=256):
+    from msd_pytorch_b200 import _lib
+
+    d = _lib.MsdTensor()
+    d.data = ptr
+    d.ndim = len(shape)
+    st = 1
+    dense = []
+    for s in reversed(shape):
+        dense.insert(0, st)
+        st *= s
+    for k, s in enumerate(shape):
+        d.size[k] = s
+        d.stride[k] = (strides or dense)[k]
+    return d
+
+
+def test_c_abi_argument_errors_need_no_gpu():
+    from msd_pytorch_b200 import _lib
+
+    L = _lib.lib
+    a, b = _desc((1, 2, 4, 4)), _desc((1, 1, 4, 4))
+    # dilation 0 and dilation > size  (msd_custom_convolutions.cpp:39-52)
+    assert L.msd_conv_forward(0, a, 256, 256, b, 0, 0, None) == 1
+    assert b"Dilation must be 1 or greater" in L.msd_last_error_string()
+    assert L.msd_conv_forward(0, a, 256, 256, b, 5, 0, None) == 1
+    assert b"Dilation cannot be greater" in L.msd_last_error_string()
+    # shape mismatch (msd_custom_convolutions.cpp:69-83)
+    assert L.msd_conv_relu_forward(0, a, 256, 256, _desc((1, 1, 4, 5)), 1, 0, None) == 1
+    assert L.msd_conv_relu_forward(0, a, 256, 256, _desc((2, 1, 4, 4)), 1, 0, None) == 1
+    # rank mismatch, bad dtype, null pointers
+    assert L.msd_conv_forward(0, a, 256, 256, _desc((1, 1, 1, 4, 4)), 1, 0, None) == 1
+    assert L.msd_conv_forward(7, a, 256, 256, b, 1, 0, None) == 2
+    assert L.msd_conv_forward(0, a, None, 256, b, 1, 0, None) == 1
+    # misaligned workspace
+    assert L.msd_conv_backward_k(0, b, a, 256, 1, 13, 1 << 20, 0, None) == 3
+    # block: channel count must be c_in + depth*width
+    ptrs = (ctypes.c_void_p * 2)(256, 256)
+    dil = (ctypes.c_int * 2)(1, 1)
+    assert L.msd_block_forward(0, _desc((1, 4, 4, 4)), 1, 2, 1, ptrs, 256, dil, 0, None) == 1
+    assert L.msd_workspace_bytes(0, 4, 1 << 20, 100, 1) > 0
