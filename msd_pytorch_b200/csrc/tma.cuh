@@ -1,0 +1,104 @@
+// Thin inline-PTX wrappers for the sm_100a asynchronous-copy machinery used by the tuned
+// kernels: mbarriers, 1-D bulk copies (cp.async.bulk) and tiled TMA loads
+// (cp.async.bulk.tensor).  No cluster multicast is used anywhere.
+//
+// Every wait is bounded: after kWaitLimit polls the waiter records a time-out in the
+// device status word and carries on (see wait_parity), so a protocol error can never hang
+// the GPU.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace msd {
+namespace tma {
+
+// Device status word: 0 = fine; otherwise the code of the first wait that ran out.
+// One copy per device that loads the library; read and cleared by msd_device_status().
+extern __device__ int g_device_status;
+
+constexpr uint32_t kWaitLimit = 1u << 24;      // polls of try_wait (each waits up to ~ms internally)
+constexpr uint32_t kAbortWaitLimit = 1u << 10; // once a time-out happened, later waits give up quickly
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+// Makes mbarrier initialisation visible to the asynchronous proxy before any copy uses it.
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait for the phase with the given parity.  `abort_flag` is a shared-memory word
+// of the block: once any thread's wait ran out, all later waits in the block use the short
+// limit, the block keeps its control flow (so every barrier is still reached) and skips its
+// global stores; the host sees the code in g_device_status.
+__device__ __forceinline__ void wait_parity(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int code) {
+    uint32_t limit = *abort_flag ? kAbortWaitLimit : kWaitLimit;
+    for (uint32_t i = 0; i < limit; ++i) {
+        if (mbar_try_wait(bar, parity)) return;
+        if ((i & 1023u) == 1023u && *abort_flag) limit = kAbortWaitLimit;
+    }
+    *abort_flag = 1;
+    atomicCAS(&g_device_status, 0, code);
+}
+
+// 1-D bulk copy global -> shared; completion is signalled on `bar` as transaction bytes.
+// Both addresses must be 16-byte aligned and `bytes` a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst_smem)),
+                 "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Tiled TMA loads (no multicast).  Coordinates are innermost first.  The innermost
+// coordinate times the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tensor_g2s_4d(void *dst_smem, const CUtensorMap *map, int c0, int c1, int c2, int c3, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(
+            smem_u32(dst_smem)),
+        "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+__device__ __forceinline__ void tensor_g2s_5d(void *dst_smem, const CUtensorMap *map, int c0, int c1, int c2, int c3, int c4, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(
+            smem_u32(dst_smem)),
+        "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
+
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+// Named barrier among `count` threads (count a multiple of 32); id 1..15.
+__device__ __forceinline__ void named_barrier(int id, int count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
+
+}  // namespace tma
+}  // namespace msd
