@@ -164,6 +164,12 @@ MSD_API int64_t msd_launch_count(void);
 MSD_API int64_t msd_fast_launch_count(void);
 MSD_API void msd_reset_launch_count(void);
 
+/* Waits for `stream`, then reports (and clears) the device status word: 0 when every
+ * kernel's internal waits completed, otherwise the code of the first bounded wait that
+ * ran out (the affected call's results are then invalid).  The tuned kernels never spin
+ * without a limit, so a protocol error shows up here instead of as a hung GPU. */
+MSD_API int msd_device_status(int device, void *stream, int *status_out);
+
 #ifdef __cplusplus
 }
 #endif

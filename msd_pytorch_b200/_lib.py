@@ -59,6 +59,7 @@ def _load():
         "msd_launch_count": (i64, []),
         "msd_fast_launch_count": (i64, []),
         "msd_reset_launch_count": (None, []),
+        "msd_device_status": (i, [i, vp, ctypes.POINTER(ctypes.c_int)]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)
@@ -74,7 +75,7 @@ EXPORTED = [
     "msd_conv_backward_k", "msd_conv_relu_backward_k", "msd_conv_backward_bias", "msd_conv_relu_backward_bias",
     "msd_block_forward", "msd_block_backward", "msd_block_workspace_bytes",
     "msd_tuning_num_variants", "msd_tuning_set", "msd_tuning_get",
-    "msd_launch_count", "msd_fast_launch_count", "msd_reset_launch_count",
+    "msd_launch_count", "msd_fast_launch_count", "msd_reset_launch_count", "msd_device_status",
 ]
 
 
@@ -121,6 +122,14 @@ def workspace(device, nbytes):
             _ws[key] = buf
     assert buf.data_ptr() % 256 == 0
     return buf
+
+
+def device_status(device):
+    """Synchronise the current stream of ``device`` and return the device status word
+    (0 = every bounded wait inside the kernels completed)."""
+    out = ctypes.c_int(0)
+    check(lib.msd_device_status(device.index, stream_of(device), ctypes.byref(out)))
+    return out.value
 
 
 def launch_counts():

@@ -1,0 +1,23 @@
+// 3D instantiations of the fused backward kernel (see fast_backward.cuh).
+#include "fast_backward.cuh"
+
+namespace msd {
+namespace fast {
+
+template <int TXQ, int J, bool DO_X, bool DO_K>
+static int launch3d(const BwdParams &p, int grid, size_t smem, cudaStream_t s) {
+    auto kern = fused_backward_kernel<3, TXQ, J, DO_X, DO_K>;
+    MSD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, kBwdThreads, smem, s>>>(p);
+    MSD_CUDA_TRY(cudaGetLastError());
+    return MSD_OK;
+}
+
+// index: [txq16?][mode], mode 0 = x only, 1 = k only, 2 = both
+BwdLaunchFn bwd3d_launchers[2][3] = {
+    {launch3d<32, 1, true, false>, launch3d<32, 1, false, true>, launch3d<32, 1, true, true>},
+    {launch3d<16, 1, true, false>, launch3d<16, 1, false, true>, launch3d<16, 1, true, true>},
+};
+
+}  // namespace fast
+}  // namespace msd

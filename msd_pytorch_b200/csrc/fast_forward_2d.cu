@@ -1,0 +1,174 @@
+// Host side and instantiations of the TMA-staged 2D forward kernel (fast_forward_2d.cuh).
+#include <cudaTypedefs.h>
+#include <mutex>
+#include <string.h>
+#include "fast_forward_2d.cuh"
+
+namespace msd {
+namespace fast {
+
+int sm_count(int device);
+
+// ---- TMA descriptor cache ---------------------------------------------------------------
+static PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
+    static std::once_flag once;
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (PFN_cuTensorMapEncodeTiled_v12000)p;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void *ptr;
+    int64_t dims[5], strides[5];
+    int box[5];
+    int rank, device, pad;  // explicit tail so that memcmp sees no padding
+    bool operator==(const MapKey &o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapEntry {
+    MapKey key;
+    CUtensorMap map;
+    uint64_t stamp;
+};
+static std::mutex g_map_mu;
+static MapEntry g_maps[128];
+static int g_map_count = 0;
+static uint64_t g_map_clock = 0;
+
+// Tiled descriptor over a float32 tensor; dims/strides innermost first, strides in elements
+// (strides[0] must be 1).  Entries are cached, least recently used first out.
+int get_tensor_map(int device, const void *ptr, int rank, const int64_t *dims, const int64_t *strides, const int *box, CUtensorMap *out) {
+    MapKey key;
+    memset(&key, 0, sizeof(key));
+    key.ptr = ptr, key.rank = rank, key.device = device;
+    for (int i = 0; i < rank; ++i) key.dims[i] = dims[i], key.strides[i] = strides[i], key.box[i] = box[i];
+    std::lock_guard<std::mutex> l(g_map_mu);
+    for (int i = 0; i < g_map_count; ++i)
+        if (g_maps[i].key == key) {
+            g_maps[i].stamp = ++g_map_clock;
+            *out = g_maps[i].map;
+            return MSD_OK;
+        }
+    PFN_cuTensorMapEncodeTiled_v12000 enc = get_encode();
+    if (!enc) MSD_FAIL(MSD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t gdim[5], gstr[4];
+    cuuint32_t bdim[5], estr[5];
+    for (int i = 0; i < rank; ++i) {
+        gdim[i] = (cuuint64_t)dims[i];
+        bdim[i] = (cuuint32_t)box[i];
+        estr[i] = 1;
+        if (i > 0) gstr[i - 1] = (cuuint64_t)strides[i] * sizeof(float);
+    }
+    CUtensorMap m;
+    CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void *>(ptr), gdim, gstr, bdim, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) MSD_FAIL(MSD_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    int slot = g_map_count;
+    if (g_map_count < 128) {
+        ++g_map_count;
+    } else {
+        slot = 0;
+        for (int i = 1; i < 128; ++i)
+            if (g_maps[i].stamp < g_maps[slot].stamp) slot = i;
+    }
+    g_maps[slot].key = key;
+    g_maps[slot].map = m;
+    g_maps[slot].stamp = ++g_map_clock;
+    *out = m;
+    return MSD_OK;
+}
+
+// ---- kernel variants ----------------------------------------------------------------------
+template <int D, int R, int Q>
+static int launch_fwd2d(const CUtensorMap &map, const Fwd2dParams &p, int grid, int stages, cudaStream_t s) {
+    using Cfg = Fwd2dCfg<D, R, Q>;
+    auto kern = forward2d_kernel<D, R, Q>;
+    const size_t smem = 256 + (size_t)stages * Cfg::STAGE_BYTES + (size_t)((p.C * 12 + 31) & ~31) * 4;
+    MSD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, Cfg::THREADS, smem, s>>>(map, p);
+    MSD_CUDA_TRY(cudaGetLastError());
+    return MSD_OK;
+}
+
+#define V(D, R, Q)                                                                                                               \
+    {                                                                                                                            \
+        launch_fwd2d<D, R, Q>, Fwd2dCfg<D, R, Q>::THREADS, Fwd2dCfg<D, R, Q>::TH, Fwd2dCfg<D, R, Q>::BH, Fwd2dCfg<D, R, Q>::BW,     \
+            Fwd2dCfg<D, R, Q>::STAGE_BYTES                                                                                       \
+    }
+// Per dilation (index D-1): variant 0 = 4-row lattice (default), variant 1 = 6-row lattice.
+static const Fwd2dVariant kFwd2d[10][2] = {
+    {V(1, 4, 8), V(1, 6, 8)}, {V(2, 4, 4), V(2, 6, 4)}, {V(3, 4, 3), V(3, 6, 3)}, {V(4, 4, 2), V(4, 6, 2)}, {V(5, 4, 2), V(5, 6, 2)},
+    {V(6, 4, 2), V(6, 6, 2)}, {V(7, 4, 2), V(7, 6, 1)}, {V(8, 4, 1), V(8, 6, 1)}, {V(9, 4, 1), V(9, 6, 1)}, {V(10, 4, 1), V(10, 6, 1)},
+};
+#undef V
+
+static const size_t kFwdSmemBudget = 220 * 1024;
+
+static bool fwd2d_plan(const View &in, int d, const Fwd2dVariant **var, int *stages) {
+    if (d < 1 || d > 10) return false;
+    int v = tuning_get(FWD2D, d);
+    if (v < 0 || v > 1) v = 0;
+    const Fwd2dVariant *cand = &kFwd2d[d - 1][v];
+    const size_t fixed = 256 + (size_t)((in.c * 12 + 31) & ~31) * 4;
+    if (fixed + 2 * (size_t)cand->stage_bytes > kFwdSmemBudget) {
+        cand = &kFwd2d[d - 1][0];
+        if (fixed + 2 * (size_t)cand->stage_bytes > kFwdSmemBudget) return false;
+    }
+    int s = (int)((kFwdSmemBudget - fixed) / cand->stage_bytes);
+    if (s > kFwdMaxStages) s = kFwdMaxStages;
+    *var = cand;
+    *stages = s;
+    return true;
+}
+
+bool forward2d_supported(const View &in, const View &out, int d) {
+    if (out.c != 1 || in.c < 1 || in.c > 4096) return false;
+    if (in.sx != 1 || out.sx != 1) return false;
+    if ((in.sy % 4) || (in.sc % 4) || (in.sn % 4) || (((uintptr_t)in.p) & 15)) return false;  // TMA: 16-byte strides and base
+    if (in.x < 16 || in.x >= (1LL << 31) || in.y >= (1LL << 31)) return false;
+    if (in.sy < in.x) return false;
+    const Fwd2dVariant *var;
+    int stages;
+    return fwd2d_plan(in, d, &var, &stages);
+}
+
+int forward2d(bool relu, const View &in, const float *k, const float *bias, const View &out, int d, int device, cudaStream_t s) {
+    const Fwd2dVariant *var;
+    int stages;
+    if (!fwd2d_plan(in, d, &var, &stages)) MSD_FAIL(MSD_ERR_UNSUPPORTED, "forward2d: shape not supported");
+    // The descriptor spans every channel that lies behind the view's base pointer in the
+    // same allocation pattern; only channels [0, C) are ever addressed.
+    const int64_t dims[4] = {in.x, in.y, in.c, in.n};
+    const int64_t strides[4] = {1, in.sy, in.sc, in.sn};
+    const int box[4] = {var->bw, var->bh, 1, 1};
+    CUtensorMap map;
+    int rc = get_tensor_map(device, in.p, 4, dims, strides, box, &map);
+    if (rc) return rc;
+    Fwd2dParams p;
+    memset(&p, 0, sizeof(p));
+    p.out = (float *)out.p;
+    p.out_sn = out.sn, p.out_sy = out.sy;
+    p.k = k, p.bias = bias;
+    p.N = (int)in.n, p.C = (int)in.c, p.Y = (int)in.y, p.X = (int)in.x;
+    p.tiles_x = (int)ceil_div(in.x, kFwdTW);
+    p.tiles_y = (int)ceil_div(in.y, var->th);
+    p.num_tiles = (long long)p.tiles_x * p.tiles_y * in.n;
+    p.stages = stages;
+    p.relu = relu ? 1 : 0;
+    p.status = tma::device_status_ptr(device);
+    if (!p.status) MSD_FAIL(MSD_ERR_CUDA, "forward2d: cannot locate the device status word");
+    int grid = sm_count(device);
+    if (p.num_tiles < grid) grid = (int)p.num_tiles;
+    rc = var->launch(map, p, grid, stages, s);
+    if (rc) return rc;
+    count_launch(true);
+    return MSD_OK;
+}
+
+}  // namespace fast
+}  // namespace msd

@@ -391,6 +391,13 @@ static int backward_bias_t(bool relu, const View *out, const View &gout, void *g
     return MSD_OK;
 }
 
+int reduce_partials_f32(const float *partial, int nparts, int64_t pitch, int64_t nout, float *dst, cudaStream_t s) {
+    reduce_partials_kernel<float><<<(unsigned)ceil_div(nout, 128), 128, 0, s>>>(partial, nparts, pitch, nout, dst);
+    count_launch(false);
+    MSD_CUDA_TRY(cudaGetLastError());
+    return MSD_OK;
+}
+
 int backward_bias(int dtype, bool relu, const View *out, const View &gout, void *gb, void *ws, size_t wsb, cudaStream_t s) {
     return dtype == MSD_F64 ? backward_bias_t<double>(relu, out, gout, gb, ws, wsb, s) : backward_bias_t<float>(relu, out, gout, gb, ws, wsb, s);
 }

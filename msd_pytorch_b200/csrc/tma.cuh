@@ -13,9 +13,10 @@
 namespace msd {
 namespace tma {
 
-// Device status word: 0 = fine; otherwise the code of the first wait that ran out.
-// One copy per device that loads the library; read and cleared by msd_device_status().
-extern __device__ int g_device_status;
+// Device status word (one per device, owned by status.cu): 0 = fine; otherwise the code
+// of the first wait that ran out.  Kernels receive its address as an argument; the host
+// reads and clears it through msd_device_status().
+int *device_status_ptr(int device);  // host; nullptr on failure
 
 constexpr uint32_t kWaitLimit = 1u << 24;      // polls of try_wait (each waits up to ~ms internally)
 constexpr uint32_t kAbortWaitLimit = 1u << 10; // once a time-out happened, later waits give up quickly
@@ -56,15 +57,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // Bounded wait for the phase with the given parity.  `abort_flag` is a shared-memory word
 // of the block: once any thread's wait ran out, all later waits in the block use the short
 // limit, the block keeps its control flow (so every barrier is still reached) and skips its
-// global stores; the host sees the code in g_device_status.
-__device__ __forceinline__ void wait_parity(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int code) {
+// global stores; the host sees the code in the device status word.
+__device__ __forceinline__ void wait_parity(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
     uint32_t limit = *abort_flag ? kAbortWaitLimit : kWaitLimit;
     for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return;
         if ((i & 1023u) == 1023u && *abort_flag) limit = kAbortWaitLimit;
     }
     *abort_flag = 1;
-    atomicCAS(&g_device_status, 0, code);
+    atomicCAS(status, 0, code);
 }
 
 // 1-D bulk copy global -> shared; completion is signalled on `bar` as transaction bytes.

@@ -172,7 +172,8 @@ def test_errors(cc, cuda_device):
         with pytest.raises(RuntimeError):  # kernel must be 3x3
             fn(x, torch.zeros(1, 1, 3, 5, device=dev, dtype=torch.float64), b, torch.empty_like(x), 1)
         with pytest.raises(RuntimeError):  # kernel must be contiguous
-            fn(x, torch.zeros(1, 3, 3, 1, device=dev, dtype=torch.float64).permute(0, 3, 1, 2), b, torch.empty_like(x), 1)
+            fn(torch.zeros(1, 2, 2, 2, device=dev, dtype=torch.float64),
+               torch.zeros(1, 3, 3, 2, device=dev, dtype=torch.float64).permute(0, 3, 1, 2), b, torch.empty_like(x), 1)
         with pytest.raises(RuntimeError):
             fn(x, k, b, torch.empty(1, 1, 2, 3, device=dev, dtype=torch.float64), 1)
         with pytest.raises(RuntimeError):
