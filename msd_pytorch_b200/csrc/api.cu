@@ -81,7 +81,7 @@ static int backward_x_impl(const char *op, bool relu, int dtype, const msd_tenso
     MSD_CUDA_TRY(g.status);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == MSD_F32 && gout.c == 1) {
-        fast::BackwardArgs a{relu ? &out : nullptr, &gout, nullptr, &gin, (const float *)kernel, nullptr, nullptr, nd, d, nullptr, 0};
+        fast::BackwardArgs a{relu ? &out : nullptr, &gout, nullptr, &gin, (const float *)kernel, nullptr, nullptr, nd, d, nullptr, 0, nullptr};
         if (fast::backward_supported(a)) return fast::backward(a, device, s);
     }
     return generic::backward_x(dtype, relu, relu ? &out : nullptr, gout, kernel, gin, nd, d, s);
@@ -106,7 +106,7 @@ static int backward_k_impl(const char *op, bool relu, int dtype, const msd_tenso
     MSD_CUDA_TRY(g.status);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == MSD_F32 && gout.c == 1) {
-        fast::BackwardArgs a{relu ? &out : nullptr, &gout, &in, nullptr, nullptr, (float *)grad_kernel, nullptr, nd, d, ws, wsb};
+        fast::BackwardArgs a{relu ? &out : nullptr, &gout, &in, nullptr, nullptr, (float *)grad_kernel, nullptr, nd, d, ws, wsb, nullptr};
         if (fast::backward_supported(a)) return fast::backward(a, device, s);
     }
     return generic::backward_k(dtype, relu, relu ? &out : nullptr, gout, in, grad_kernel, nd, d, ws, wsb, s);
@@ -241,8 +241,15 @@ int msd_block_forward(int dtype, const msd_tensor_t *result, int c_in, int depth
 }
 
 size_t msd_block_workspace_bytes(int dtype, int ndim, int64_t voxels, int c_in, int depth, int width) {
+    // Room for every layer's partial sums, so that all second-pass reductions of a block can
+    // run as one kernel at the end (capped; a smaller buffer only makes them run in batches).
     const int64_t n_max = c_in + (int64_t)(depth - 1) * width;
-    return msd_workspace_bytes(dtype, ndim, voxels, n_max, width);
+    const size_t one = msd_workspace_bytes(dtype, ndim, voxels, n_max, width);
+    size_t all = 0;
+    for (int i = 0; i < depth; ++i) all += fast::backward_workspace_bytes(ndim == 5 ? 3 : 2, c_in + (int64_t)i * width);
+    const size_t cap = (size_t)256 << 20;
+    if (all > cap) all = cap;
+    return all > one ? all : one;
 }
 
 int msd_block_backward(int dtype, const msd_tensor_t *result, const msd_tensor_t *gradients, int c_in, int depth, int width,
@@ -259,6 +266,8 @@ int msd_block_backward(int dtype, const msd_tensor_t *result, const msd_tensor_t
     MSD_CUDA_TRY(g.status);
     cudaStream_t s = (cudaStream_t)stream;
     const size_t es = dtype == MSD_F64 ? 8 : 4;
+    fast::ReduceList pending;
+    pending.count = 0, pending.ws_used = 0;
     for (int i = depth - 1; i >= 0; --i) {
         const int64_t n_i = c_in + (int64_t)i * width;
         View out = channel_slice(r, n_i, width, es);
@@ -269,17 +278,19 @@ int msd_block_backward(int dtype, const msd_tensor_t *result, const msd_tensor_t
         void *gk = grad_weights ? grad_weights[i] : nullptr;
         void *gb = grad_bias ? (char *)grad_bias + (size_t)i * width * es : nullptr;
         if (dtype == MSD_F32 && width == 1) {
-            fast::BackwardArgs a{&out, &gout, &in, &gin, (const float *)weights[i], (float *)gk, (float *)gb, nd, d, workspace, workspace_bytes};
+            fast::BackwardArgs a{&out, &gout, &in, &gin, (const float *)weights[i], (float *)gk, (float *)gb, nd, d, workspace, workspace_bytes, &pending};
             if (fast::backward_supported(a)) {
                 if ((rc = fast::backward(a, device, s))) return rc;
                 continue;
             }
         }
+        // the generic kernels use the workspace from its start: finish pending reductions first
+        if ((rc = fast::flush_reductions(&pending, s))) return rc;
         if ((rc = generic::backward_x(dtype, true, &out, gout, weights[i], gin, nd, d, s))) return rc;
         if (gk && (rc = generic::backward_k(dtype, true, &out, gout, in, gk, nd, d, workspace, workspace_bytes, s))) return rc;
         if (gb && (rc = generic::backward_bias(dtype, true, &out, gout, gb, workspace, workspace_bytes, s))) return rc;
     }
-    return MSD_OK;
+    return fast::flush_reductions(&pending, s);
 }
 
 int msd_tuning_num_variants(int family) { return fast::num_variants(family); }

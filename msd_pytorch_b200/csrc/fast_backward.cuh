@@ -18,8 +18,8 @@
 // (2 x 27) FMAs per voxel, one 128-bit store.  No halo is needed for the C-channel
 // streams; only the single channel m is read with a halo, once per tile.
 //
-// Data movement (sm_100a): a producer warp issues 1-D bulk asynchronous copies
-// (cp.async.bulk, completion on mbarriers) of the tile rows of in[c] and gin[c] into a
+// Data movement (sm_100a): a producer warp issues tiled TMA loads
+// (cp.async.bulk.tensor, completion on mbarriers) of the tile of in[c] and of gin[c] into a
 // multi-stage shared-memory ring, running up to `stages` channels ahead, across tile
 // boundaries; eight consumer warps read the ring with 128-bit shared loads and write
 // gin[c] straight from registers with 128-bit global stores.  Blocks are persistent and
@@ -107,7 +107,8 @@ __device__ __forceinline__ float warp_reduce_scatter(float (&v)[NV], int lane) {
 __device__ __forceinline__ float4 ld4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
 
 template <int ND, int TXQ, int J, bool DO_X, bool DO_K>
-__global__ void __launch_bounds__(kBwdThreads, 1) fused_backward_kernel(const BwdParams p) {
+__global__ void __launch_bounds__(kBwdThreads, 1)
+fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_gin, const BwdParams p) {
     using T = BwdTraits<ND>;
     constexpr int RT = T::RT, TAPS = T::TAPS, TAPS_PAD = T::TAPS_PAD, NV = T::NV;
     constexpr int TX = TXQ * 4;
@@ -126,7 +127,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fused_backward_kernel(const Bw
     const int TXP = TX + 2 * p.Dp;
     float *wacc = wsm + (DO_X ? p.C * TAPS_PAD : 0);
     float *rows = wacc + (DO_K ? kConsumerWarps * p.C * TAPS_PAD : 0);
-    float *ring = rows + RT * TR * TXP;
+    // ring stages are TMA destinations: 128-byte aligned
+    float *ring = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(rows + RT * TR * TXP) + 127) & ~uintptr_t(127));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int S = p.stages;
@@ -154,36 +156,35 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fused_backward_kernel(const Bw
 
     if (warp == kConsumerWarps) {
         // ------------------------------ producer warp ------------------------------
-        uint32_t it = 0;
-        for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
-            const int tx_i = (int)(tile % p.tiles_x);
-            const int ty_i = (int)((tile / p.tiles_x) % p.tiles_y);
-            const long long nz = tile / tiles_per_plane;
-            const int z = (int)(nz % p.Z), n = (int)(nz / p.Z);
-            const int x0 = tx_i * TX, y0 = ty_i * TR;
-            const int rows_valid = min(TR, p.Y - y0);
-            const uint32_t row_bytes = (uint32_t)min(TX, p.X - x0) * 4u;
-            const float *in_base = DO_K ? p.in + n * p.in_sn + z * p.in_sz + (int64_t)y0 * p.in_sy + x0 : nullptr;
-            const float *gi_base = DO_X ? p.gin + n * p.gi_sn + z * p.gi_sz + (int64_t)y0 * p.gi_sy + x0 : nullptr;
-            for (int c = 0; c < p.C; ++c, ++it) {
-                const int s = it % S;
-                const uint32_t ph = (it / S) & 1u;
-                if (it >= (uint32_t)S) tma::wait_parity(&empty[s], ph ^ 1u, abort_flag, p.status, 1);
-                if (lane == 0) tma::mbar_arrive_expect_tx(&full[s], row_bytes * rows_valid * NARR);
-                __syncwarp();
-                float *stage = ring + s * STAGE;
-                for (int rr = lane; rr < rows_valid * NARR; rr += 32) {
-                    const int arr = rr / rows_valid, r = rr - arr * rows_valid;
-                    const float *src;
-                    if (DO_K && arr == 0)
-                        src = in_base + c * p.in_sc + (int64_t)r * p.in_sy;
-                    else
-                        src = gi_base + c * p.gi_sc + (int64_t)r * p.gi_sy;
-                    tma::bulk_g2s(stage + arr * TR * TX + r * TX, src, row_bytes, &full[s]);
+        // One tiled TMA load per array and channel: the TR x TX tile of in[c] and of gin[c].
+        // Parts of the box beyond the image are zero-filled by the TMA unit.
+        if (lane == 0) {
+            if (DO_K) tma::prefetch_tensormap(&map_in);
+            if (DO_X) tma::prefetch_tensormap(&map_gin);
+            uint32_t it = 0;
+            for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+                const int tx_i = (int)(tile % p.tiles_x);
+                const int ty_i = (int)((tile / p.tiles_x) % p.tiles_y);
+                const long long nz = tile / tiles_per_plane;
+                const int z = (int)(nz % p.Z), n = (int)(nz / p.Z);
+                const int x0 = tx_i * TX, y0 = ty_i * TR;
+                for (int c = 0; c < p.C; ++c, ++it) {
+                    const int s = it % S;
+                    const uint32_t ph = (it / S) & 1u;
+                    if (it >= (uint32_t)S) tma::wait_parity(&empty[s], ph ^ 1u, abort_flag, p.status, 1);
+                    tma::mbar_arrive_expect_tx(&full[s], (uint32_t)(STAGE * 4));
+                    float *stage = ring + s * STAGE;
+                    if (ND == 3) {
+                        if (DO_K) tma::tensor_g2s_5d(stage, &map_in, x0, y0, z, c, n, &full[s]);
+                        if (DO_X) tma::tensor_g2s_5d(stage + (DO_K ? TR * TX : 0), &map_gin, x0, y0, z, c, n, &full[s]);
+                    } else {
+                        if (DO_K) tma::tensor_g2s_4d(stage, &map_in, x0, y0, c, n, &full[s]);
+                        if (DO_X) tma::tensor_g2s_4d(stage + (DO_K ? TR * TX : 0), &map_gin, x0, y0, c, n, &full[s]);
+                    }
                 }
             }
         }
-        return;  // all copies this warp issued are awaited by the consumers below
+        return;  // every box this warp requested is awaited by the consumers below
     }
 
     // -------------------------------- consumer warps --------------------------------
@@ -202,36 +203,65 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fused_backward_kernel(const Bw
         const float *go_n = p.gout + n * p.go_sn;
         const float *out_n = p.out ? p.out + n * p.out_sn : nullptr;
         const int quads = TXP / 4;
-        for (int rowid = warp; rowid < RT * TR; rowid += kConsumerWarps) {
-            const int rt = rowid / TR, r = rowid - rt * TR;
-            const int y = y0 + r;
-            int zs[2], ys[2], nzs, nys = 0;
-            if (ND == 3) {
-                nzs = adjoint_sources_dev(z, rt / 3, p.d, p.Z, zs);
-            } else {
-                nzs = 1;
-                zs[0] = 0;
+        // Each warp stages RT*TR/8 rows, three at a time so that six independent 128-bit
+        // global loads are in flight per thread.
+        constexpr int ROWS_PER_WARP = RT * TR / kConsumerWarps;
+        constexpr int U = 3;
+        static_assert(ROWS_PER_WARP % U == 0, "rows per warp must be a multiple of the batch");
+        for (int rb = 0; rb < ROWS_PER_WARP; rb += U) {
+            int zs[U][2], ys[U][2], nzs[U], nys[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int rowid = warp + kConsumerWarps * (rb + u);
+                const int rt = rowid / TR, r = rowid - rt * TR;
+                const int y = y0 + r;
+                nys[u] = 0;
+                if (ND == 3) {
+                    nzs[u] = adjoint_sources_dev(z, rt / 3, p.d, p.Z, zs[u]);
+                } else {
+                    nzs[u] = 1;
+                    zs[u][0] = 0;
+                }
+                if (y < p.Y) nys[u] = adjoint_sources_dev(y, (ND == 3) ? rt % 3 : rt, p.d, p.Y, ys[u]);
+                if (nzs[u] == 0) nys[u] = 0;
             }
-            if (y < p.Y) nys = adjoint_sources_dev(y, (ND == 3) ? rt % 3 : rt, p.d, p.Y, ys);
-            float *dst = rows + (int64_t)rowid * TXP;
             for (int q4 = lane; q4 < quads; q4 += 32) {
                 const int px = x0 - p.Dp + 4 * q4;
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (px >= 0 && px < p.X) {
-                    for (int a = 0; a < nzs; ++a)
-                        for (int b = 0; b < nys; ++b) {
-                            float4 g = ld4(go_n + zs[a] * p.go_sz + (int64_t)ys[b] * p.go_sy + px);
-                            if (out_n) {
-                                const float4 o = ld4(out_n + zs[a] * p.out_sz + (int64_t)ys[b] * p.out_sy + px);
-                                g.x = o.x > 0.f ? g.x : 0.f;
-                                g.y = o.y > 0.f ? g.y : 0.f;
-                                g.z = o.z > 0.f ? g.z : 0.f;
-                                g.w = o.w > 0.f ? g.w : 0.f;
-                            }
-                            acc.x += g.x, acc.y += g.y, acc.z += g.z, acc.w += g.w;
-                        }
+                const bool inside = px >= 0 && px < p.X;
+                float4 g[U], o[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    g[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    o[u] = make_float4(1.f, 1.f, 1.f, 1.f);
+                    if (inside && nys[u] > 0) {
+                        g[u] = ld4(go_n + zs[u][0] * p.go_sz + (int64_t)ys[u][0] * p.go_sy + px);
+                        if (out_n) o[u] = ld4(out_n + zs[u][0] * p.out_sz + (int64_t)ys[u][0] * p.out_sy + px);
+                    }
                 }
-                *reinterpret_cast<float4 *>(dst + 4 * q4) = acc;
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    float4 acc;
+                    acc.x = o[u].x > 0.f ? g[u].x : 0.f;
+                    acc.y = o[u].y > 0.f ? g[u].y : 0.f;
+                    acc.z = o[u].z > 0.f ? g[u].z : 0.f;
+                    acc.w = o[u].w > 0.f ? g[u].w : 0.f;
+                    if (inside && nzs[u] * nys[u] > 1) {  // folded sources: border rows only
+                        for (int a = 0; a < nzs[u]; ++a)
+                            for (int b = (a == 0 ? 1 : 0); b < nys[u]; ++b) {
+                                float4 g2 = ld4(go_n + zs[u][a] * p.go_sz + (int64_t)ys[u][b] * p.go_sy + px);
+                                if (out_n) {
+                                    const float4 o2 = ld4(out_n + zs[u][a] * p.out_sz + (int64_t)ys[u][b] * p.out_sy + px);
+                                    g2.x = o2.x > 0.f ? g2.x : 0.f;
+                                    g2.y = o2.y > 0.f ? g2.y : 0.f;
+                                    g2.z = o2.z > 0.f ? g2.z : 0.f;
+                                    g2.w = o2.w > 0.f ? g2.w : 0.f;
+                                }
+                                acc.x += g2.x, acc.y += g2.y, acc.z += g2.z, acc.w += g2.w;
+                            }
+                    }
+                    const int rowid = warp + kConsumerWarps * (rb + u);
+                    *reinterpret_cast<float4 *>(rows + (int64_t)rowid * TXP + 4 * q4) = acc;
+                }
             }
         }
         tma::named_barrier(1, kConsumers);
@@ -278,10 +308,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fused_backward_kernel(const Bw
 #pragma unroll
             for (int j = 0; j < J; ++j) {
                 const int idx = (rpass + RPP * j) * TX + 4 * xq;
-                if (DO_K) {
-                    a[j] = ld4(stage + idx);
-                    if (!valid[j]) a[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-                }
+                if (DO_K) a[j] = ld4(stage + idx);  // zero outside the image (TMA fill)
                 if (DO_X) g[j] = ld4(stage + (DO_K ? TR * TX : 0) + idx);
             }
             __syncwarp();
@@ -358,7 +385,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fused_backward_kernel(const Bw
 }
 
 // Host-side launcher of one instantiation; defined in fast_backward_impl.cuh.
-typedef int (*BwdLaunchFn)(const BwdParams &, int grid, size_t smem, cudaStream_t);
+typedef int (*BwdLaunchFn)(const CUtensorMap &, const CUtensorMap &, const BwdParams &, int grid, size_t smem, cudaStream_t);
 
 }  // namespace fast
 }  // namespace msd

@@ -8,12 +8,13 @@ int reduce_partials_f32(const float *partial, int nparts, int64_t pitch, int64_t
 }
 namespace fast {
 
+int get_tensor_map(int device, const void *ptr, int rank, const int64_t *dims, const int64_t *strides, const int *box, CUtensorMap *out);
 extern BwdLaunchFn bwd2d_launchers[2][2][3];
 extern BwdLaunchFn bwd3d_launchers[2][3];
 
 static const int kMaxFastDilation = 16;
 static const size_t kSmemBudget = 200 * 1024;
-static const int kMaxGrid = 148 * 4;
+static const int kMaxGrid = 256;
 
 int sm_count(int device) {
     static std::mutex mu;
@@ -30,6 +31,7 @@ int sm_count(int device) {
 
 static bool aligned_view(const View *v) {
     if (!v) return true;
+    if (v->sy < v->x || v->x >= (1LL << 31) || v->y >= (1LL << 31) || v->z >= (1LL << 31)) return false;
     return v->sx == 1 && (v->sn % 4) == 0 && (v->sc % 4) == 0 && (v->sy % 4) == 0 && (v->sz % 4) == 0 && (((uintptr_t)v->p) & 15) == 0;
 }
 
@@ -54,8 +56,8 @@ static bool plan(const BackwardArgs &a, BwdPlan *pl) {
     }
     for (; j >= 1; --j) {
         const int TR = (kConsumers / (TX / 4)) * j;
-        const size_t fixed = 256 + (size_t)4 * ((do_x ? C * TAPS_PAD : 0) + (do_k ? kConsumerWarps * C * TAPS_PAD : 0) +
-                                                 (int64_t)RT * TR * (TX + 2 * Dp));
+        const size_t fixed = 256 + 128 + (size_t)4 * ((do_x ? C * TAPS_PAD : 0) + (do_k ? kConsumerWarps * C * TAPS_PAD : 0) +
+                                                       (int64_t)RT * TR * (TX + 2 * Dp));
         const size_t stage = (size_t)4 * ((do_x ? 1 : 0) + (do_k ? 1 : 0)) * TR * TX;
         if (fixed + 2 * stage > kSmemBudget) continue;
         int s = (int)((kSmemBudget - fixed) / stage);
@@ -91,6 +93,51 @@ bool backward_supported(const BackwardArgs &a) {
 size_t backward_workspace_bytes(int nd, int64_t c_in) {
     const int taps = nd == 3 ? 27 : 9;
     return (size_t)kMaxGrid * (c_in * taps + 64) * sizeof(float) + 512;
+}
+
+struct ReduceTable {
+    ReduceEntry e[ReduceList::kMax];
+};
+
+// Pass two for a table of layers: dst[j] += sum over the blocks' partials, block order fixed.
+__global__ void __launch_bounds__(128) reduce_table_kernel(const __grid_constant__ ReduceTable t) {
+    const ReduceEntry &e = t.e[blockIdx.y];
+    const int j = blockIdx.x * 128 + threadIdx.x;
+    const int nk = e.pk ? e.nk : 0;
+    if (j < nk) {
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        int q = 0;
+        for (; q + 3 < e.nparts; q += 4) {
+            s0 += e.pk[(int64_t)(q + 0) * nk + j];
+            s1 += e.pk[(int64_t)(q + 1) * nk + j];
+            s2 += e.pk[(int64_t)(q + 2) * nk + j];
+            s3 += e.pk[(int64_t)(q + 3) * nk + j];
+        }
+        for (; q < e.nparts; ++q) s0 += e.pk[(int64_t)q * nk + j];
+        e.gk[j] += (s0 + s1) + (s2 + s3);
+    } else if (j == nk && e.pb) {
+        float s0 = 0.f;
+        for (int q = 0; q < e.nparts; ++q) s0 += e.pb[q];
+        e.gb[0] += s0;
+    }
+}
+
+int flush_reductions(ReduceList *list, cudaStream_t s) {
+    if (!list || list->count == 0) return MSD_OK;
+    ReduceTable t;
+    int max_n = 1;
+    for (int i = 0; i < list->count; ++i) {
+        t.e[i] = list->e[i];
+        const int n = (list->e[i].pk ? list->e[i].nk : 0) + 1;
+        if (n > max_n) max_n = n;
+    }
+    dim3 grid((unsigned)ceil_div(max_n, 128), (unsigned)list->count);
+    reduce_table_kernel<<<grid, 128, 0, s>>>(t);
+    count_launch(false);
+    list->count = 0;
+    list->ws_used = 0;
+    MSD_CUDA_TRY(cudaGetLastError());
+    return MSD_OK;
 }
 
 int backward(const BackwardArgs &a, int device, cudaStream_t s) {
@@ -130,20 +177,49 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
     int grid = sm_count(device);
     if (p.num_tiles < grid) grid = (int)p.num_tiles;
     if (grid > kMaxGrid) grid = kMaxGrid;
-    char *ws = (char *)a.ws;
-    if (do_k) p.part_k = (float *)ws;
     const bool do_b = a.gb != nullptr;
-    if (do_b) p.part_b = (float *)(ws + (((size_t)grid * C * taps * sizeof(float) + 255) & ~(size_t)255));
+    const size_t need_k = do_k ? (((size_t)grid * C * taps * sizeof(float) + 255) & ~(size_t)255) : 0;
+    const size_t need = need_k + (do_b ? (((size_t)grid * sizeof(float) + 255) & ~(size_t)255) : 0);
+    if (a.defer && (a.defer->count == ReduceList::kMax || a.defer->ws_used + need > a.wsb)) {
+        int rcf = flush_reductions(a.defer, s);
+        if (rcf) return rcf;
+    }
+    if (need > a.wsb) MSD_FAIL(MSD_ERR_WORKSPACE, "fused backward: workspace of %zu bytes needed, %zu given", need, a.wsb);
+    char *ws = (char *)a.ws + (a.defer ? a.defer->ws_used : 0);
+    if (do_k) p.part_k = (float *)ws;
+    if (do_b) p.part_b = (float *)(ws + need_k);
+    // TMA descriptors of the two streamed tensors (a missing one aliases the other; unused).
+    CUtensorMap map_in, map_gin;
+    {
+        const int rank = a.nd == 3 ? 5 : 4;
+        int box[5] = {TX, TR, 1, 1, 1};
+        for (int which = 0; which < 2; ++which) {
+            const View *v = which == 0 ? (do_k ? a.in : a.gin) : (do_x ? a.gin : a.in);
+            int64_t dims[5], strides[5];
+            if (a.nd == 3) {
+                dims[0] = v->x, dims[1] = v->y, dims[2] = v->z, dims[3] = v->c, dims[4] = v->n;
+                strides[0] = 1, strides[1] = v->sy, strides[2] = v->sz, strides[3] = v->sc, strides[4] = v->sn;
+            } else {
+                dims[0] = v->x, dims[1] = v->y, dims[2] = v->c, dims[3] = v->n, dims[4] = 1;
+                strides[0] = 1, strides[1] = v->sy, strides[2] = v->sc, strides[3] = v->sn, strides[4] = 0;
+            }
+            int rc2 = get_tensor_map(device, v->p, rank, dims, strides, box, which == 0 ? &map_in : &map_gin);
+            if (rc2) return rc2;
+        }
+    }
     const int mode = do_x && do_k ? 2 : (do_k ? 1 : 0);
     BwdLaunchFn fn = a.nd == 3 ? bwd3d_launchers[pl.txq16][mode] : bwd2d_launchers[pl.txq16][pl.j - 1][mode];
-    int rc = fn(p, grid, pl.smem, s);
+    int rc = fn(map_in, map_gin, p, grid, pl.smem, s);
     if (rc) return rc;
     count_launch(true);
-    if (do_k) {
-        if ((rc = generic::reduce_partials_f32(p.part_k, grid, C * taps, C * taps, a.gk, s))) return rc;
-    }
-    if (do_b) {
-        if ((rc = generic::reduce_partials_f32(p.part_b, grid, 1, 1, a.gb, s))) return rc;
+    if (do_k || do_b) {
+        ReduceList single;
+        ReduceList *list = a.defer ? a.defer : &single;
+        if (!a.defer) single.count = 0, single.ws_used = 0;
+        ReduceEntry &e = list->e[list->count++];
+        e.pk = p.part_k, e.pb = p.part_b, e.gk = a.gk, e.gb = a.gb, e.nparts = grid, e.nk = (int)(C * taps);
+        list->ws_used += need;
+        if (!a.defer && (rc = flush_reductions(list, s))) return rc;
     }
     return MSD_OK;
 }

@@ -9,7 +9,7 @@ int forward2d(bool relu, const View &in, const float *k, const float *bias, cons
 
 int num_variants(int family) {
     switch (family) {
-        case FWD2D: return 2;  // 4-row / 6-row lattice
+        case FWD2D: return 3;  // lattice rows x column segments per thread
         case BWD2D: return 2;  // 4 / 8 voxels per thread
         default: return 1;
     }

@@ -84,10 +84,10 @@ int get_tensor_map(int device, const void *ptr, int rank, const int64_t *dims, c
 }
 
 // ---- kernel variants ----------------------------------------------------------------------
-template <int D, int R, int Q>
+template <int D, int R, int Q, int K>
 static int launch_fwd2d(const CUtensorMap &map, const Fwd2dParams &p, int grid, int stages, cudaStream_t s) {
-    using Cfg = Fwd2dCfg<D, R, Q>;
-    auto kern = forward2d_kernel<D, R, Q>;
+    using Cfg = Fwd2dCfg<D, R, Q, K>;
+    auto kern = forward2d_kernel<D, R, Q, K>;
     const size_t smem = 256 + (size_t)stages * Cfg::STAGE_BYTES + (size_t)((p.C * 12 + 31) & ~31) * 4;
     MSD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<grid, Cfg::THREADS, smem, s>>>(map, p);
@@ -95,15 +95,18 @@ static int launch_fwd2d(const CUtensorMap &map, const Fwd2dParams &p, int grid, 
     return MSD_OK;
 }
 
-#define V(D, R, Q)                                                                                                               \
-    {                                                                                                                            \
-        launch_fwd2d<D, R, Q>, Fwd2dCfg<D, R, Q>::THREADS, Fwd2dCfg<D, R, Q>::TH, Fwd2dCfg<D, R, Q>::BH, Fwd2dCfg<D, R, Q>::BW,     \
-            Fwd2dCfg<D, R, Q>::STAGE_BYTES                                                                                       \
+#define V(D, R, Q, K)                                                                                                       \
+    {                                                                                                                       \
+        launch_fwd2d<D, R, Q, K>, Fwd2dCfg<D, R, Q, K>::THREADS, Fwd2dCfg<D, R, Q, K>::TH, Fwd2dCfg<D, R, Q, K>::BH,            \
+            Fwd2dCfg<D, R, Q, K>::BW, Fwd2dCfg<D, R, Q, K>::STAGE_BYTES                                                       \
     }
-// Per dilation (index D-1): variant 0 = 4-row lattice (default), variant 1 = 6-row lattice.
-static const Fwd2dVariant kFwd2d[10][2] = {
-    {V(1, 4, 8), V(1, 6, 8)}, {V(2, 4, 4), V(2, 6, 4)}, {V(3, 4, 3), V(3, 6, 3)}, {V(4, 4, 2), V(4, 6, 2)}, {V(5, 4, 2), V(5, 6, 2)},
-    {V(6, 4, 2), V(6, 6, 2)}, {V(7, 4, 2), V(7, 6, 1)}, {V(8, 4, 1), V(8, 6, 1)}, {V(9, 4, 1), V(9, 6, 1)}, {V(10, 4, 1), V(10, 6, 1)},
+// Per dilation (index D-1): variant 0 = 4-row lattice, 4 column segments per thread;
+// variant 1 = 4-row lattice, 2 segments (twice the warps); variant 2 = 6-row lattice, 4 segments.
+static const Fwd2dVariant kFwd2d[10][3] = {
+    {V(1, 4, 8, 4), V(1, 4, 8, 2), V(1, 6, 8, 4)},  {V(2, 4, 4, 4), V(2, 4, 4, 2), V(2, 6, 4, 4)},  {V(3, 4, 3, 4), V(3, 4, 3, 2), V(3, 6, 3, 4)},
+    {V(4, 4, 2, 4), V(4, 4, 2, 2), V(4, 6, 2, 4)},  {V(5, 4, 2, 4), V(5, 4, 2, 2), V(5, 6, 2, 4)},  {V(6, 4, 2, 4), V(6, 4, 2, 2), V(6, 6, 2, 4)},
+    {V(7, 4, 2, 4), V(7, 4, 2, 2), V(7, 6, 1, 4)},  {V(8, 4, 1, 4), V(8, 4, 1, 2), V(8, 6, 1, 4)},  {V(9, 4, 1, 4), V(9, 4, 1, 2), V(9, 6, 1, 4)},
+    {V(10, 4, 1, 4), V(10, 4, 1, 2), V(10, 6, 1, 4)},
 };
 #undef V
 
@@ -112,7 +115,7 @@ static const size_t kFwdSmemBudget = 220 * 1024;
 static bool fwd2d_plan(const View &in, int d, const Fwd2dVariant **var, int *stages) {
     if (d < 1 || d > 10) return false;
     int v = tuning_get(FWD2D, d);
-    if (v < 0 || v > 1) v = 0;
+    if (v < 0 || v > 2) v = 0;
     const Fwd2dVariant *cand = &kFwd2d[d - 1][v];
     const size_t fixed = 256 + (size_t)((in.c * 12 + 31) & ~31) * 4;
     if (fixed + 2 * (size_t)cand->stage_bytes > kFwdSmemBudget) {

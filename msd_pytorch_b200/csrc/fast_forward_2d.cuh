@@ -11,16 +11,16 @@
 //
 // Compute: the tile has Q*R*D rows and 128 columns.  A warp owns the rows
 // {base + i + j*D, j < R} of one residue class i modulo D ("row lattice") and its 32 lanes
-// own 4 column segments 32 apart.  Output rows j and j+1 of a lattice share two of their
-// three input rows, so per channel a thread loads (R+2)*3*4 values from shared memory for
-// R*9*4 FMAs.  All shared loads are scalar with lanes on consecutive columns (conflict
+// own K column segments 32 apart.  Output rows j and j+1 of a lattice share two of their
+// three input rows, so per channel a thread loads (R+2)*3*K values from shared memory for
+// R*9*K FMAs.  All shared loads are scalar with lanes on consecutive columns (conflict
 // free for any D).
 //
 // Reflection: rows are handled for free by giving every thread the (possibly reflected)
-// shared-memory row of each of its R+2 lattice rows in a register.  Columns that fall
-// outside the image (only in tiles that touch the left or right border) are patched in
-// shared memory after the box has landed: D cells per row and side are copied from their
-// mirror cells, which always lie inside the same box.
+// shared-memory row of each of its R+2 lattice rows in a register.  Columns: in tiles that
+// touch the left or right image border the x-D tap of the first segment and the x+D taps
+// use per-thread offsets that point at the mirror cell (always inside the same box); all
+// other tiles run a copy of the loop with compile-time offsets.
 #pragma once
 #include "common.cuh"
 #include "kernels.h"
@@ -30,7 +30,6 @@ namespace msd {
 namespace fast {
 
 constexpr int kFwdTW = 128;  // tile width
-constexpr int kFwdK = 4;     // column segments per thread
 constexpr int kFwdMaxStages = 8;
 
 struct Fwd2dParams {
@@ -46,9 +45,10 @@ struct Fwd2dParams {
     int *status;
 };
 
-template <int D, int R, int Q>
+template <int D, int R, int Q, int K>
 struct Fwd2dCfg {
-    static constexpr int NCW = Q * D;               // compute warps
+    static constexpr int XW = kFwdTW / (32 * K);    // warps side by side along x
+    static constexpr int NCW = Q * D * XW;          // compute warps
     static constexpr int THREADS = NCW * 32 + 32;   // + producer warp
     static constexpr int TH = Q * R * D;            // tile rows
     static constexpr int DP = (D + 3) & ~3;
@@ -58,12 +58,42 @@ struct Fwd2dCfg {
     static constexpr int STAGE = STAGE_BYTES / 4;
 };
 
-template <int D, int R, int Q>
-__global__ void __launch_bounds__(Fwd2dCfg<D, R, Q>::THREADS, 1)
+// One input channel's contribution to a thread's R x K accumulators.  `rp[m]` points at the
+// thread's first column in lattice row m of the box; BORDER selects run-time column
+// offsets for the taps that may leave the image.
+template <int D, int R, int K, bool BORDER>
+__device__ __forceinline__ void fwd2d_channel(float (&acc)[R][K], const float *st, const int (&rowoff)[R + 2], const float *wsm_c, int dl,
+                                              const int (&dr)[K]) {
+    const float4 *wp = reinterpret_cast<const float4 *>(wsm_c);
+    const float4 w0 = wp[0], w1 = wp[1], w2 = wp[2];
+    const float w[9] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w, w2.x};
+#pragma unroll
+    for (int m = 0; m < R + 2; ++m) {
+        const float *rp = st + rowoff[m];
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+            const float a = (BORDER && k == 0) ? rp[dl] : rp[32 * k - D];
+            const float b = rp[32 * k];
+            const float cc = BORDER ? rp[32 * k + dr[k]] : rp[32 * k + D];
+#pragma unroll
+            for (int j = 0; j < R; ++j) {
+                const int t = m - j;  // tap row of output row j that reads lattice row m
+                if (t >= 0 && t <= 2) {
+                    acc[j][k] = fmaf(w[t * 3 + 0], a, acc[j][k]);
+                    acc[j][k] = fmaf(w[t * 3 + 1], b, acc[j][k]);
+                    acc[j][k] = fmaf(w[t * 3 + 2], cc, acc[j][k]);
+                }
+            }
+        }
+    }
+}
+
+template <int D, int R, int Q, int K>
+__global__ void __launch_bounds__(Fwd2dCfg<D, R, Q, K>::THREADS, 1)
 forward2d_kernel(const __grid_constant__ CUtensorMap map, const Fwd2dParams p) {
-    using Cfg = Fwd2dCfg<D, R, Q>;
-    constexpr int NCW = Cfg::NCW, TH = Cfg::TH, DP = Cfg::DP, BW = Cfg::BW, BH = Cfg::BH, STAGE = Cfg::STAGE;
-    constexpr int TW = kFwdTW, K = kFwdK;
+    using Cfg = Fwd2dCfg<D, R, Q, K>;
+    constexpr int NCW = Cfg::NCW, XW = Cfg::XW, TH = Cfg::TH, DP = Cfg::DP, BW = Cfg::BW, BH = Cfg::BH, STAGE = Cfg::STAGE;
+    constexpr int TW = kFwdTW;
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw);
@@ -113,7 +143,9 @@ forward2d_kernel(const __grid_constant__ CUtensorMap map, const Fwd2dParams p) {
     }
 
     // -------------------------------- compute warps --------------------------------
-    const int q = warp / D, i = warp - q * D;
+    const int xw = warp % XW, u = warp / XW;
+    const int q = u / D, i = u - q * D;
+    const int cb = xw * 32 * K + lane;  // first column of this thread inside the tile
     const float bias = p.bias[0];
     uint32_t it = 0;
     for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
@@ -132,9 +164,17 @@ forward2d_kernel(const __grid_constant__ CUtensorMap map, const Fwd2dParams p) {
             if (y >= p.Y) y = 2 * p.Y - 1 - y;
             int br = y - (y0 - D);
             br = br < 0 ? 0 : (br > BH - 1 ? BH - 1 : br);
-            rowoff[m] = br * BW + DP + lane;
+            rowoff[m] = br * BW + DP + cb;
         }
-        const bool patch_l = (x0 == 0), patch_r = (x0 + TW + D > p.X);
+        // Column offsets of the taps that may leave the image (see fwd2d_channel).
+        const bool border = (x0 == 0) || (x0 + TW + D > p.X);
+        int dl = -D, dr[K];
+        if (x0 == 0 && cb < D) dl = D - 1 - 2 * cb;  // x - D < 0 mirrors to D - 1 - x
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+            const int x = x0 + cb + 32 * k;
+            dr[k] = (x < p.X && x + D >= p.X) ? 2 * p.X - 1 - 2 * x - D : D;  // x + D >= X mirrors to 2X - 1 - (x + D)
+        }
 
         float acc[R][K];
 #pragma unroll
@@ -145,40 +185,11 @@ forward2d_kernel(const __grid_constant__ CUtensorMap map, const Fwd2dParams p) {
         for (int c = 0; c < p.C; ++c, ++it) {
             const int s = it % S;
             tma::wait_parity(&full[s], (it / S) & 1u, abort_flag, p.status, 4);
-            float *st = ring + (size_t)s * STAGE;
-            if (patch_l || patch_r) {
-                // mirror the D out-of-image columns of every box row on the affected side(s)
-                const int ctid = tid;  // compute threads are 0 .. NCW*32-1
-                for (int e = ctid; e < BH * D; e += NCW * 32) {
-                    const int r = e / D, jj = e - r * D;
-                    if (patch_l) st[r * BW + DP - 1 - jj] = st[r * BW + DP + jj];  // x = -1-jj  <-  x = jj
-                    if (patch_r) {
-                        const int xr = p.X - x0 + DP;  // box column of image x = X
-                        if (xr + jj < BW) st[r * BW + xr + jj] = st[r * BW + xr - 1 - jj];  // x = X+jj  <-  X-1-jj
-                    }
-                }
-                tma::named_barrier(1, NCW * 32);
-            }
-            const float4 *wp = reinterpret_cast<const float4 *>(wsm + c * 12);
-            const float4 w0 = wp[0], w1 = wp[1], w2 = wp[2];
-            const float w[9] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w, w2.x};
-#pragma unroll
-            for (int m = 0; m < R + 2; ++m) {
-                const float *rp = st + rowoff[m];
-#pragma unroll
-                for (int k = 0; k < K; ++k) {
-                    const float a = rp[32 * k - D], b = rp[32 * k], cc = rp[32 * k + D];
-#pragma unroll
-                    for (int j = 0; j < R; ++j) {
-                        const int t = m - j;  // tap row of output row j that reads lattice row m
-                        if (t >= 0 && t <= 2) {
-                            acc[j][k] = fmaf(w[t * 3 + 0], a, acc[j][k]);
-                            acc[j][k] = fmaf(w[t * 3 + 1], b, acc[j][k]);
-                            acc[j][k] = fmaf(w[t * 3 + 2], cc, acc[j][k]);
-                        }
-                    }
-                }
-            }
+            const float *st = ring + (size_t)s * STAGE;
+            if (border)
+                fwd2d_channel<D, R, K, true>(acc, st, rowoff, wsm + c * 12, dl, dr);
+            else
+                fwd2d_channel<D, R, K, false>(acc, st, rowoff, wsm + c * 12, dl, dr);
             __syncwarp();
             if (lane == 0) tma::mbar_arrive(&empty[s]);
         }
@@ -191,7 +202,7 @@ forward2d_kernel(const __grid_constant__ CUtensorMap map, const Fwd2dParams p) {
                 if (y < p.Y) {
 #pragma unroll
                     for (int k = 0; k < K; ++k) {
-                        const int x = x0 + lane + 32 * k;
+                        const int x = x0 + cb + 32 * k;
                         float v = acc[j][k];
                         if (p.relu) v = v > 0.f ? v : 0.f;
                         if (x < p.X) ob[(int64_t)y * p.out_sy + x] = v;

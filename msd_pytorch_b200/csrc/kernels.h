@@ -32,6 +32,23 @@ int forward(bool relu, const View &in, const float *k, const float *bias, const 
 //   gk[c,:] += <in[c] shifted, m>      (if gk; deterministic two-pass)
 //   gb      += sum m                   (if gb)
 // `out` may be null (no gate).  `in` may be null when gk is null.
+// Deferred second pass of the weight/bias gradient reduction: the fused backward of every
+// layer of a block appends one entry, and one table-driven kernel adds all partials at the end.
+struct ReduceEntry {
+    const float *pk;  // [nparts][nk] partials of the weight gradient, or null
+    const float *pb;  // [nparts] partials of the bias gradient, or null
+    float *gk;        // accumulated into
+    float *gb;        // accumulated into
+    int nparts, nk;
+};
+struct ReduceList {
+    static const int kMax = 64;
+    ReduceEntry e[kMax];
+    int count;
+    size_t ws_used;
+};
+int flush_reductions(ReduceList *list, cudaStream_t s);
+
 struct BackwardArgs {
     const View *out;   // [N,1,...] ReLU output (gate) or null
     const View *gout;  // [N,1,...]
@@ -43,6 +60,7 @@ struct BackwardArgs {
     int nd, d;
     void *ws;
     size_t wsb;
+    ReduceList *defer;  // null: reduce right after the layer's kernel
 };
 bool backward_supported(const BackwardArgs &a);
 size_t backward_workspace_bytes(int nd, int64_t c_in);

@@ -155,7 +155,7 @@ def test_module_gradcheck_and_final_layer(cuda_device):
         c.bias.data.copy_(fl.linear.bias.data)
         z = torch.randn(2, 4, *sp, device=dev)
         # 5e-3: cuDNN may run the comparison convolutions in TF32
-            torch.testing.assert_close(fl(z), c(z), rtol=5e-3, atol=5e-3)
+        torch.testing.assert_close(fl(z), c(z), rtol=5e-3, atol=5e-3)
 
 
 def test_untrained_module_outputs_zero_and_validation(cuda_device):

@@ -132,3 +132,28 @@ def test_fused_block_backward_matches_separate_ops(cuda_device, nd):
     block_backward_(res, g3, 1, dil, ws, gw3, gb3)
     torch.cuda.synchronize()
     assert torch.equal(g1[:, :1], g3[:, :1]) and torch.equal(gb1, gb3) and all(torch.equal(a, b) for a, b in zip(gw1, gw3))
+
+
+@pytest.mark.parametrize("variant", [0, 1, 2])
+@pytest.mark.parametrize("d", [1, 2, 3, 4, 5, 6, 7, 8, 9, 10])
+def test_forward_launch_variants(cc, cuda_device, d, variant):
+    """Every tile-shape variant of the TMA forward gives the oracle's result, including
+    tiles on all four image borders, ragged last tiles and several tiles per block."""
+    from msd_pytorch_b200 import _lib
+    from oracle import msd_oracle as O
+
+    dev = cuda_device
+    assert _lib.lib.msd_tuning_num_variants(_lib.FAMILY_FWD2D) == 3
+    _lib.check(_lib.lib.msd_tuning_set(_lib.FAMILY_FWD2D, d, variant))
+    try:
+        x, k, b, go = util.make_op_inputs(3, 4, 1, (150, 300), torch.float32, 40 + d, dev)
+        y = torch.empty_like(go, device=dev)
+        before = _counts()
+        cc.conv_relu_forward(x.to(dev), k.to(dev), b.to(dev), y, d)
+        assert _status(dev) == 0
+        assert _counts()[1] - before[1] == 1
+        y_o = torch.empty_like(go, dtype=torch.float64)
+        O.conv_relu_forward(x.double(), k.double(), b.double(), y_o, d)
+        assert_close(y, y_o, 1e-4, "forward variant %d" % variant)
+    finally:
+        _lib.lib.msd_tuning_set(_lib.FAMILY_FWD2D, d, -1)
