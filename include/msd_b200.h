@@ -164,6 +164,21 @@ MSD_API int64_t msd_launch_count(void);
 MSD_API int64_t msd_fast_launch_count(void);
 MSD_API void msd_reset_launch_count(void);
 
+/* No counterpart in the reference: msd_conv_relu_backward_k for callers that cannot
+ * allocate device memory (a plugin inside another framework's memory pool, a latency-bound
+ * serving loop, a host with a fixed memory plan).  It takes no workspace: the partial sums
+ * live in a 4 MiB array built into the library, which every GPU that loads the library
+ * holds until exit.  Shapes that need more return MSD_ERR_LIMIT and launch nothing.  All
+ * calls on a device share the array, so calls that may overlap on the GPU race; calls on
+ * one stream are safe.  The first call on each device resolves the array's address and
+ * should be made outside any stream capture.  Allocates nothing. */
+MSD_API int msd_conv_relu_backward_k_noalloc(int dtype, const msd_tensor_t *output, const msd_tensor_t *grad_output,
+                                             const msd_tensor_t *input, void *grad_kernel, int dilation,
+                                             int device, void *stream);
+
+/* Size in bytes of the built-in scratch array used by msd_conv_relu_backward_k_noalloc. */
+MSD_API size_t msd_noalloc_scratch_bytes(void);
+
 /* Waits for `stream`, then reports (and clears) the device status word: 0 when every
  * kernel's internal waits completed, otherwise the code of the first bounded wait that
  * ran out (the affected call's results are then invalid).  The tuned kernels never spin

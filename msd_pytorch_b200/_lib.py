@@ -60,6 +60,8 @@ def _load():
         "msd_fast_launch_count": (i64, []),
         "msd_reset_launch_count": (None, []),
         "msd_device_status": (i, [i, vp, ctypes.POINTER(ctypes.c_int)]),
+        "msd_conv_relu_backward_k_noalloc": (i, [i, T, T, T, vp, i, i, vp]),
+        "msd_noalloc_scratch_bytes": (sz, []),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)
@@ -76,6 +78,7 @@ EXPORTED = [
     "msd_block_forward", "msd_block_backward", "msd_block_workspace_bytes",
     "msd_tuning_num_variants", "msd_tuning_set", "msd_tuning_get",
     "msd_launch_count", "msd_fast_launch_count", "msd_reset_launch_count", "msd_device_status",
+    "msd_conv_relu_backward_k_noalloc", "msd_noalloc_scratch_bytes",
 ]
 
 
