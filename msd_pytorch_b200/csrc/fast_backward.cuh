@@ -22,8 +22,11 @@
 // (cp.async.bulk.tensor, completion on mbarriers) of the tile of in[c] and of gin[c] into a
 // multi-stage shared-memory ring, running up to `stages` channels ahead, across tile
 // boundaries; eight consumer warps read the ring with 128-bit shared loads and write
-// gin[c] straight from registers with 128-bit global stores.  Blocks are persistent and
-// take tiles in a fixed round-robin order.
+// gin[c] straight from registers with 128-bit global stores.  The halo rows of gout and
+// out that the NEXT tile's M_t need (3 or 9 row-shifted boxes each, out-of-image parts
+// zero-filled) are TMA loads as well, issued one tile ahead into their own buffer, so no
+// thread ever waits for a plain global load on the critical path.  Blocks are persistent
+// and take tiles in a fixed round-robin order.
 //
 // Weight gradient reduction (deterministic, two passes): per channel each warp sums its
 // threads' 9 (27) partials with a shuffle reduce-scatter and adds them to its own slot in
@@ -33,6 +36,16 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "tma.cuh"
+
+#ifdef MSD_BWD_TIMING
+// Developer instrumentation (off in normal builds): per-phase clock sums of block 0, thread 0.
+#define MSD_T(var) const long long var = clock64()
+#define MSD_TADD(slot, a, b) \
+    if (blockIdx.x == 0 && threadIdx.x == 0 && p.timing) p.timing[slot] += (unsigned long long)((b) - (a))
+#else
+#define MSD_T(var)
+#define MSD_TADD(slot, a, b)
+#endif
 
 namespace msd {
 namespace fast {
@@ -60,6 +73,7 @@ struct BwdParams {
     long long num_tiles;
     int stages;
     int *status;
+    unsigned long long *timing;  // developer instrumentation, null in normal builds
 };
 
 template <int ND>
@@ -106,9 +120,17 @@ __device__ __forceinline__ float warp_reduce_scatter(float (&v)[NV], int lane) {
 
 __device__ __forceinline__ float4 ld4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
 
+// Blocks per SM the kernel is compiled for: the 4-voxel-per-thread 2D variant is small
+// enough for two resident blocks, so that one block's tile set-up overlaps the other's streaming.
+template <int ND, int J>
+struct BwdOccupancy {
+    static constexpr int kBlocksPerSM = (ND == 2 && J == 1) ? 2 : 1;
+};
+
 template <int ND, int TXQ, int J, bool DO_X, bool DO_K>
-__global__ void __launch_bounds__(kBwdThreads, 1)
-fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_gin, const BwdParams p) {
+__global__ void __launch_bounds__(kBwdThreads, BwdOccupancy<ND, J>::kBlocksPerSM)
+fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_gin,
+                      const __grid_constant__ CUtensorMap map_gout, const __grid_constant__ CUtensorMap map_out, const BwdParams p) {
     using T = BwdTraits<ND>;
     constexpr int RT = T::RT, TAPS = T::TAPS, TAPS_PAD = T::TAPS_PAD, NV = T::NV;
     constexpr int TX = TXQ * 4;
@@ -121,14 +143,20 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
     extern __shared__ __align__(128) unsigned char smem_raw[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw);
     uint64_t *empty = full + kMaxStages;
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(empty + kMaxStages);
+    uint64_t *halo_full = empty + kMaxStages;  // the halo rows of a tile have landed
+    uint64_t *halo_empty = halo_full + 1;      // all consumer warps are done with them
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(halo_empty + 1);
     float *red = reinterpret_cast<float *>(smem_raw + 192);  // 16 floats
-    float *wsm = reinterpret_cast<float *>(smem_raw + 256);
     const int TXP = TX + 2 * p.Dp;
+    const bool gate = p.out != nullptr;
+    // TMA destinations first (128-byte aligned): halo rows of gout (turned into the folded
+    // rows of m in place), halo rows of out, then the ring.
+    float *rows = reinterpret_cast<float *>(smem_raw + 256);
+    const int halo_floats = ((RT * TR * TXP + 31) & ~31);
+    float *orows = rows + halo_floats;
+    float *ring = orows + (gate ? halo_floats : 0);
+    float *wsm = ring + (size_t)p.stages * STAGE;
     float *wacc = wsm + (DO_X ? p.C * TAPS_PAD : 0);
-    float *rows = wacc + (DO_K ? kConsumerWarps * p.C * TAPS_PAD : 0);
-    // ring stages are TMA destinations: 128-byte aligned
-    float *ring = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(rows + RT * TR * TXP) + 127) & ~uintptr_t(127));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int S = p.stages;
@@ -138,6 +166,8 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
             tma::mbar_init(&full[s], 1);
             tma::mbar_init(&empty[s], kConsumerWarps);
         }
+        tma::mbar_init(halo_full, 1);
+        tma::mbar_init(halo_empty, kConsumerWarps);
         *abort_flag = 0;
         tma::fence_barrier_init();
     }
@@ -161,13 +191,42 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
         if (lane == 0) {
             if (DO_K) tma::prefetch_tensormap(&map_in);
             if (DO_X) tma::prefetch_tensormap(&map_gin);
-            uint32_t it = 0;
-            for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+            tma::prefetch_tensormap(&map_gout);
+            if (gate) tma::prefetch_tensormap(&map_out);
+            const uint32_t halo_bytes = (uint32_t)(RT * TR * TXP * 4) * (gate ? 2u : 1u);
+            // Halo rows of one tile: row tap (tz, ty) reads the rows shifted by d (1 - t).
+            auto issue_halo = [&](long long tile) {
+                const int tx_i = (int)(tile % p.tiles_x);
+                const int ty_i = (int)((tile / p.tiles_x) % p.tiles_y);
+                const long long nz = tile / tiles_per_plane;
+                const int z = (int)(nz % p.Z), n = (int)(nz / p.Z);
+                const int bx = tx_i * TX - p.Dp, y0 = ty_i * TR;
+                tma::mbar_arrive_expect_tx(halo_full, halo_bytes);
+#pragma unroll
+                for (int rt = 0; rt < RT; ++rt) {
+                    const int ty = (ND == 3) ? rt % 3 : rt, tz = (ND == 3) ? rt / 3 : 1;
+                    const int by = y0 + p.d * (1 - ty), bz = z + p.d * (1 - tz);
+                    float *dg = rows + rt * TR * TXP, *dout = orows + rt * TR * TXP;
+                    if (ND == 3) {
+                        tma::tensor_g2s_5d(dg, &map_gout, bx, by, bz, 0, n, halo_full);
+                        if (gate) tma::tensor_g2s_5d(dout, &map_out, bx, by, bz, 0, n, halo_full);
+                    } else {
+                        tma::tensor_g2s_4d(dg, &map_gout, bx, by, 0, n, halo_full);
+                        if (gate) tma::tensor_g2s_4d(dout, &map_out, bx, by, 0, n, halo_full);
+                    }
+                }
+            };
+            uint32_t it = 0, tcount = 0;
+            if ((long long)blockIdx.x < p.num_tiles) issue_halo(blockIdx.x);
+            for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++tcount) {
                 const int tx_i = (int)(tile % p.tiles_x);
                 const int ty_i = (int)((tile / p.tiles_x) % p.tiles_y);
                 const long long nz = tile / tiles_per_plane;
                 const int z = (int)(nz % p.Z), n = (int)(nz / p.Z);
                 const int x0 = tx_i * TX, y0 = ty_i * TR;
+                // The next tile's halo rows go out once this tile's first `S` channels are
+                // requested: by then the ring is what the producer waits on anyway.
+                const int halo_at = (p.C < S ? p.C : S) - 1;
                 for (int c = 0; c < p.C; ++c, ++it) {
                     const int s = it % S;
                     const uint32_t ph = (it / S) & 1u;
@@ -181,6 +240,10 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
                         if (DO_K) tma::tensor_g2s_4d(stage, &map_in, x0, y0, c, n, &full[s]);
                         if (DO_X) tma::tensor_g2s_4d(stage + (DO_K ? TR * TX : 0), &map_gin, x0, y0, c, n, &full[s]);
                     }
+                    if (c == halo_at && tile + gridDim.x < p.num_tiles) {
+                        tma::wait_parity(halo_empty, tcount & 1u, abort_flag, p.status, 5);
+                        issue_halo(tile + gridDim.x);
+                    }
                 }
             }
         }
@@ -189,105 +252,96 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
 
     // -------------------------------- consumer warps --------------------------------
     const int xq = tid % TXQ, rpass = tid / TXQ;
-    uint32_t it = 0;
+    uint32_t it = 0, tcount = 0;
     float bsum = 0.f;
-    for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+    for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++tcount) {
         const int tx_i = (int)(tile % p.tiles_x);
         const int ty_i = (int)((tile / p.tiles_x) % p.tiles_y);
         const long long nz = tile / tiles_per_plane;
         const int z = (int)(nz % p.Z), n = (int)(nz / p.Z);
         const int x0 = tx_i * TX, y0 = ty_i * TR;
 
-        // ---- stage the folded rows of m for the RT row taps of this tile ----
-        tma::named_barrier(1, kConsumers);  // the previous tile's reads of `rows` are done
+        // ---- turn the halo rows (landed by TMA) into the folded rows of m, in place ----
+        MSD_T(t0);
+        tma::wait_parity(halo_full, tcount & 1u, abort_flag, p.status, 6);
+        MSD_T(t1);
         const float *go_n = p.gout + n * p.go_sn;
-        const float *out_n = p.out ? p.out + n * p.out_sn : nullptr;
+        const float *out_n = gate ? p.out + n * p.out_sn : nullptr;
         const int quads = TXP / 4;
-        // Each warp stages RT*TR/8 rows, three at a time so that six independent 128-bit
-        // global loads are in flight per thread.
-        constexpr int ROWS_PER_WARP = RT * TR / kConsumerWarps;
-        constexpr int U = 3;
-        static_assert(ROWS_PER_WARP % U == 0, "rows per warp must be a multiple of the batch");
-        for (int rb = 0; rb < ROWS_PER_WARP; rb += U) {
-            int zs[U][2], ys[U][2], nzs[U], nys[U];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int rowid = warp + kConsumerWarps * (rb + u);
+        // Rows within d of a y (z) border also collect a mirrored source row; those few are
+        // fetched with plain loads.
+        const bool fold_rows = (y0 < p.d) || (y0 + TR + p.d > p.Y) || (ND == 3 && (z < p.d || z + p.d >= p.Z));
+        for (int item = tid; item < RT * TR * quads; item += kConsumers) {
+            const int rowid = item / quads, q4 = item - rowid * quads;
+            float4 g = *reinterpret_cast<const float4 *>(rows + rowid * TXP + 4 * q4);
+            if (gate) {
+                const float4 o = *reinterpret_cast<const float4 *>(orows + rowid * TXP + 4 * q4);
+                g.x = o.x > 0.f ? g.x : 0.f;
+                g.y = o.y > 0.f ? g.y : 0.f;
+                g.z = o.z > 0.f ? g.z : 0.f;
+                g.w = o.w > 0.f ? g.w : 0.f;
+            }
+            if (fold_rows) {
                 const int rt = rowid / TR, r = rowid - rt * TR;
-                const int y = y0 + r;
-                nys[u] = 0;
-                if (ND == 3) {
-                    nzs[u] = adjoint_sources_dev(z, rt / 3, p.d, p.Z, zs[u]);
-                } else {
-                    nzs[u] = 1;
-                    zs[u][0] = 0;
-                }
-                if (y < p.Y) nys[u] = adjoint_sources_dev(y, (ND == 3) ? rt % 3 : rt, p.d, p.Y, ys[u]);
-                if (nzs[u] == 0) nys[u] = 0;
-            }
-            for (int q4 = lane; q4 < quads; q4 += 32) {
-                const int px = x0 - p.Dp + 4 * q4;
-                const bool inside = px >= 0 && px < p.X;
-                float4 g[U], o[U];
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    g[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    o[u] = make_float4(1.f, 1.f, 1.f, 1.f);
-                    if (inside && nys[u] > 0) {
-                        g[u] = ld4(go_n + zs[u][0] * p.go_sz + (int64_t)ys[u][0] * p.go_sy + px);
-                        if (out_n) o[u] = ld4(out_n + zs[u][0] * p.out_sz + (int64_t)ys[u][0] * p.out_sy + px);
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    float4 acc;
-                    acc.x = o[u].x > 0.f ? g[u].x : 0.f;
-                    acc.y = o[u].y > 0.f ? g[u].y : 0.f;
-                    acc.z = o[u].z > 0.f ? g[u].z : 0.f;
-                    acc.w = o[u].w > 0.f ? g[u].w : 0.f;
-                    if (inside && nzs[u] * nys[u] > 1) {  // folded sources: border rows only
-                        for (int a = 0; a < nzs[u]; ++a)
-                            for (int b = (a == 0 ? 1 : 0); b < nys[u]; ++b) {
-                                float4 g2 = ld4(go_n + zs[u][a] * p.go_sz + (int64_t)ys[u][b] * p.go_sy + px);
-                                if (out_n) {
-                                    const float4 o2 = ld4(out_n + zs[u][a] * p.out_sz + (int64_t)ys[u][b] * p.out_sy + px);
-                                    g2.x = o2.x > 0.f ? g2.x : 0.f;
-                                    g2.y = o2.y > 0.f ? g2.y : 0.f;
-                                    g2.z = o2.z > 0.f ? g2.z : 0.f;
-                                    g2.w = o2.w > 0.f ? g2.w : 0.f;
-                                }
-                                acc.x += g2.x, acc.y += g2.y, acc.z += g2.z, acc.w += g2.w;
+                const int y = y0 + r, px = x0 - p.Dp + 4 * q4;
+                int zs[2], ys[2], nzs = 1, nys = 0;
+                zs[0] = 0;
+                if (ND == 3) nzs = adjoint_sources_dev(z, rt / 3, p.d, p.Z, zs);
+                if (y < p.Y && nzs > 0) nys = adjoint_sources_dev(y, (ND == 3) ? rt % 3 : rt, p.d, p.Y, ys);
+                if (px >= 0 && px < p.X && nzs * nys > 0) {
+                    // The TMA box holds the direct source (zero when it lies outside); add the
+                    // others.  The direct source is the first entry exactly when it is inside.
+                    const int dy = y - p.d * (((ND == 3) ? rt % 3 : rt) - 1);
+                    const int dz = (ND == 3) ? z - p.d * (rt / 3 - 1) : 0;
+                    for (int a = 0; a < nzs; ++a)
+                        for (int b = 0; b < nys; ++b) {
+                            if (ys[b] == dy && (ND != 3 || zs[a] == dz)) continue;  // already there
+                            float4 g2 = ld4(go_n + zs[a] * p.go_sz + (int64_t)ys[b] * p.go_sy + px);
+                            if (out_n) {
+                                const float4 o2 = ld4(out_n + zs[a] * p.out_sz + (int64_t)ys[b] * p.out_sy + px);
+                                g2.x = o2.x > 0.f ? g2.x : 0.f;
+                                g2.y = o2.y > 0.f ? g2.y : 0.f;
+                                g2.z = o2.z > 0.f ? g2.z : 0.f;
+                                g2.w = o2.w > 0.f ? g2.w : 0.f;
                             }
-                    }
-                    const int rowid = warp + kConsumerWarps * (rb + u);
-                    *reinterpret_cast<float4 *>(rows + (int64_t)rowid * TXP + 4 * q4) = acc;
+                            g.x += g2.x, g.y += g2.y, g.z += g2.z, g.w += g2.w;
+                        }
                 }
             }
+            *reinterpret_cast<float4 *>(rows + rowid * TXP + 4 * q4) = g;
         }
+        MSD_T(t2);
         tma::named_barrier(1, kConsumers);
+        MSD_T(t3);
 
         // ---- per-thread M_t for its P voxels ----
         float M[TAPS][P];
         bool valid[J];
+        const bool fold_x = (x0 < p.d) || (x0 + TX + p.d > p.X);
 #pragma unroll
         for (int j = 0; j < J; ++j) {
             const int r = rpass + RPP * j;
             valid[j] = (y0 + r) < p.Y && (x0 + 4 * xq) < p.X;
 #pragma unroll
             for (int rt = 0; rt < RT; ++rt) {
-                const float *row = rows + (int64_t)(rt * TR + r) * TXP + p.Dp;  // row[i] <-> image x = x0 + i
+                const float *row = rows + (rt * TR + r) * TXP + p.Dp;  // row[i] <-> image x = x0 + i
+                const float4 ctr = *reinterpret_cast<const float4 *>(row + 4 * xq);
+                const float cv[4] = {ctr.x, ctr.y, ctr.z, ctr.w};
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int i = 4 * xq + e;
-                    const int q = x0 + i;
                     float m0 = row[i + p.d];
                     float m2 = row[i - p.d];
-                    if (q < p.X) {
-                        if (q <= p.d - 1) m0 += row[p.d - 1 - q - x0];
-                        if (q >= p.X - p.d) m2 += row[2 * p.X - 1 - q - p.d - x0];
+                    if (fold_x) {  // block-uniform: only tiles next to the left / right border
+                        const int q = x0 + i;
+                        const bool f0 = q < p.X && q <= p.d - 1, f2 = q < p.X && q >= p.X - p.d;
+                        const float v0 = row[f0 ? p.d - 1 - q - x0 : i];
+                        const float v2 = row[f2 ? 2 * p.X - 1 - q - p.d - x0 : i];
+                        m0 += f0 ? v0 : 0.f;
+                        m2 += f2 ? v2 : 0.f;
                     }
                     M[rt * 3 + 0][j * 4 + e] = m0;
-                    M[rt * 3 + 1][j * 4 + e] = row[i];
+                    M[rt * 3 + 1][j * 4 + e] = cv[e];
                     M[rt * 3 + 2][j * 4 + e] = m2;
                 }
             }
@@ -296,10 +350,16 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
                 for (int e = 0; e < 4; ++e) bsum += M[(RT / 2) * 3 + 1][j * 4 + e];
             }
         }
+        // this warp no longer needs the halo rows: the producer may load the next tile's
+        // (the fence orders this thread's shared-memory accesses before the TMA writes)
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) tma::mbar_arrive(halo_empty);
 
         float *gi_tile = DO_X ? p.gin + n * p.gi_sn + z * p.gi_sz + (int64_t)y0 * p.gi_sy + x0 + 4 * xq : nullptr;
 
         // ---- stream the C input channels past the registers ----
+        MSD_T(t4);
         for (int c = 0; c < p.C; ++c, ++it) {
             const int s = it % S;
             tma::wait_parity(&full[s], (it / S) & 1u, abort_flag, p.status, 2);
@@ -355,6 +415,13 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
                 if (lane < TAPS) wacc[(warp * p.C + c) * TAPS_PAD + lane] += tot;
             }
         }
+        MSD_T(t5);
+        MSD_TADD(0, t0, t1);  // barrier at tile start
+        MSD_TADD(1, t1, t2);  // staging of the folded rows
+        MSD_TADD(2, t2, t3);  // barrier after staging
+        MSD_TADD(3, t3, t4);  // M registers
+        MSD_TADD(4, t4, t5);  // channel loop
+        MSD_TADD(5, 0, 1);    // tiles
     }
 
     // ---- block epilogue: fixed-order sums of the warp slots, one partial per block ----
@@ -385,7 +452,7 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
 }
 
 // Host-side launcher of one instantiation; defined in fast_backward_impl.cuh.
-typedef int (*BwdLaunchFn)(const CUtensorMap &, const CUtensorMap &, const BwdParams &, int grid, size_t smem, cudaStream_t);
+typedef int (*BwdLaunchFn)(const CUtensorMap *maps, const BwdParams &, int grid, size_t smem, cudaStream_t);  // maps: in, gin, gout, out
 
 }  // namespace fast
 }  // namespace msd

@@ -5,10 +5,10 @@ namespace msd {
 namespace fast {
 
 template <int TXQ, int J, bool DO_X, bool DO_K>
-static int launch3d(const CUtensorMap &mi, const CUtensorMap &mg, const BwdParams &p, int grid, size_t smem, cudaStream_t s) {
+static int launch3d(const CUtensorMap *m, const BwdParams &p, int grid, size_t smem, cudaStream_t s) {
     auto kern = fused_backward_kernel<3, TXQ, J, DO_X, DO_K>;
     MSD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, kBwdThreads, smem, s>>>(mi, mg, p);
+    kern<<<grid, kBwdThreads, smem, s>>>(m[0], m[1], m[2], m[3], p);
     MSD_CUDA_TRY(cudaGetLastError());
     return MSD_OK;
 }

@@ -12,9 +12,20 @@ int get_tensor_map(int device, const void *ptr, int rank, const int64_t *dims, c
 extern BwdLaunchFn bwd2d_launchers[2][2][3];
 extern BwdLaunchFn bwd3d_launchers[2][3];
 
+#ifdef MSD_BWD_TIMING
+static unsigned long long *g_dbg_timing = nullptr;
+extern "C" MSD_API void msd_debug_bwd_timing(unsigned long long *out) {
+    cudaDeviceSynchronize();
+    if (g_dbg_timing) {
+        cudaMemcpy(out, g_dbg_timing, 64, cudaMemcpyDeviceToHost);
+        cudaMemset(g_dbg_timing, 0, 64);
+    }
+}
+#endif
+
 static const int kMaxFastDilation = 16;
 static const size_t kSmemBudget = 200 * 1024;
-static const int kMaxGrid = 256;
+static const int kMaxGrid = 320;
 
 int sm_count(int device) {
     static std::mutex mu;
@@ -36,7 +47,7 @@ static bool aligned_view(const View *v) {
 }
 
 struct BwdPlan {
-    int txq16, j, stages;
+    int txq16, j, stages, blocks_per_sm;
     size_t smem;
 };
 
@@ -56,14 +67,22 @@ static bool plan(const BackwardArgs &a, BwdPlan *pl) {
     }
     for (; j >= 1; --j) {
         const int TR = (kConsumers / (TX / 4)) * j;
-        const size_t fixed = 256 + 128 + (size_t)4 * ((do_x ? C * TAPS_PAD : 0) + (do_k ? kConsumerWarps * C * TAPS_PAD : 0) +
-                                                       (int64_t)RT * TR * (TX + 2 * Dp));
+        const size_t halo = (size_t)(((int64_t)RT * TR * (TX + 2 * Dp) + 31) & ~31) * (a.out ? 2 : 1);
+        const size_t fixed = 256 + (size_t)4 * ((do_x ? C * TAPS_PAD : 0) + (do_k ? kConsumerWarps * C * TAPS_PAD : 0) + halo);
         const size_t stage = (size_t)4 * ((do_x ? 1 : 0) + (do_k ? 1 : 0)) * TR * TX;
-        if (fixed + 2 * stage > kSmemBudget) continue;
-        int s = (int)((kSmemBudget - fixed) / stage);
+        // two resident blocks per SM for the small 2D variant when both fit
+        int bps = (nd == 2 && j == 1) ? 2 : 1;
+        size_t budget = bps == 2 ? (size_t)110 * 1024 : kSmemBudget;
+        if (bps == 2 && fixed + 3 * stage > budget) {
+            bps = 1;
+            budget = kSmemBudget;
+        }
+        if (fixed + 2 * stage > budget) continue;
+        int s = (int)((budget - fixed) / stage);
         if (s > kMaxStages) s = kMaxStages;
         pl->j = j;
         pl->stages = s;
+        pl->blocks_per_sm = bps;
         pl->smem = fixed + (size_t)s * stage;
         return true;
     }
@@ -174,9 +193,20 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
     p.stages = pl.stages;
     p.status = tma::device_status_ptr(device);
     if (!p.status) MSD_FAIL(MSD_ERR_CUDA, "fused backward: cannot locate the device status word");
-    int grid = sm_count(device);
-    if (p.num_tiles < grid) grid = (int)p.num_tiles;
+#ifdef MSD_BWD_TIMING
+    {
+        static unsigned long long *dbg = nullptr;
+        if (!dbg) {
+            cudaMalloc(&dbg, 64);
+            cudaMemset(dbg, 0, 64);
+        }
+        p.timing = dbg;
+        g_dbg_timing = dbg;
+    }
+#endif
+    int grid = sm_count(device) * pl.blocks_per_sm;
     if (grid > kMaxGrid) grid = kMaxGrid;
+    if (p.num_tiles < grid) grid = (int)p.num_tiles;
     const bool do_b = a.gb != nullptr;
     const size_t need_k = do_k ? (((size_t)grid * C * taps * sizeof(float) + 255) & ~(size_t)255) : 0;
     const size_t need = need_k + (do_b ? (((size_t)grid * sizeof(float) + 255) & ~(size_t)255) : 0);
@@ -188,13 +218,15 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
     char *ws = (char *)a.ws + (a.defer ? a.defer->ws_used : 0);
     if (do_k) p.part_k = (float *)ws;
     if (do_b) p.part_b = (float *)(ws + need_k);
-    // TMA descriptors of the two streamed tensors (a missing one aliases the other; unused).
-    CUtensorMap map_in, map_gin;
+    // TMA descriptors: the two streamed tensors (a missing one aliases the other and is never
+    // used) and the halo rows of gout / out (out aliases gout when there is no gate).
+    CUtensorMap maps[4];
     {
         const int rank = a.nd == 3 ? 5 : 4;
-        int box[5] = {TX, TR, 1, 1, 1};
-        for (int which = 0; which < 2; ++which) {
-            const View *v = which == 0 ? (do_k ? a.in : a.gin) : (do_x ? a.gin : a.in);
+        const View *views[4] = {do_k ? a.in : a.gin, do_x ? a.gin : a.in, a.gout, a.out ? a.out : a.gout};
+        for (int which = 0; which < 4; ++which) {
+            const View *v = views[which];
+            int box[5] = {which < 2 ? TX : TX + 2 * p.Dp, TR, 1, 1, 1};
             int64_t dims[5], strides[5];
             if (a.nd == 3) {
                 dims[0] = v->x, dims[1] = v->y, dims[2] = v->z, dims[3] = v->c, dims[4] = v->n;
@@ -203,13 +235,13 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
                 dims[0] = v->x, dims[1] = v->y, dims[2] = v->c, dims[3] = v->n, dims[4] = 1;
                 strides[0] = 1, strides[1] = v->sy, strides[2] = v->sc, strides[3] = v->sn, strides[4] = 0;
             }
-            int rc2 = get_tensor_map(device, v->p, rank, dims, strides, box, which == 0 ? &map_in : &map_gin);
+            int rc2 = get_tensor_map(device, v->p, rank, dims, strides, box, &maps[which]);
             if (rc2) return rc2;
         }
     }
     const int mode = do_x && do_k ? 2 : (do_k ? 1 : 0);
     BwdLaunchFn fn = a.nd == 3 ? bwd3d_launchers[pl.txq16][mode] : bwd2d_launchers[pl.txq16][pl.j - 1][mode];
-    int rc = fn(map_in, map_gin, p, grid, pl.smem, s);
+    int rc = fn(maps, p, grid, pl.smem, s);
     if (rc) return rc;
     count_launch(true);
     if (do_k || do_b) {
