@@ -81,13 +81,20 @@ MSD_API size_t msd_workspace_bytes(int dtype, int ndim, int64_t voxels, int64_t 
 
 /* ---- single operations: the eight functions of `msd_custom_convolutions` ---- */
 
+/* Scratch bytes the forward entry points want for these sizes (0 for 2D and for float64).
+ * The tuned 3D forward keeps three partial-sum volumes there; without a workspace
+ * (NULL / too small) 3D calls still work but run the generic kernel. */
+MSD_API size_t msd_forward_workspace_bytes(int dtype, int ndim, int64_t voxels);
+
 /* conv_forward (msd_custom_convolutions.cpp:85-116; conv2d_forward.cu:22-93, conv3d_forward.cu:22-108) */
 MSD_API int msd_conv_forward(int dtype, const msd_tensor_t *input, const void *kernel, const void *bias,
-                     const msd_tensor_t *output, int dilation, int device, void *stream);
+                     const msd_tensor_t *output, int dilation, void *workspace, size_t workspace_bytes,
+                     int device, void *stream);
 
 /* conv_relu_forward (msd_custom_convolutions.cpp:213-245; conv2d_forward.cu:95-174, conv3d_forward.cu:110-196) */
 MSD_API int msd_conv_relu_forward(int dtype, const msd_tensor_t *input, const void *kernel, const void *bias,
-                          const msd_tensor_t *output, int dilation, int device, void *stream);
+                          const msd_tensor_t *output, int dilation, void *workspace, size_t workspace_bytes,
+                          int device, void *stream);
 
 /* conv_backward_x (msd_custom_convolutions.cpp:118-148; conv2d_backward_x.cu:13-106, conv3d_backward_x.cu:13-123) */
 MSD_API int msd_conv_backward_x(int dtype, const msd_tensor_t *grad_output, const void *kernel,
@@ -124,10 +131,11 @@ MSD_API int msd_conv_relu_backward_bias(int dtype, const msd_tensor_t *output, c
  * Layer i reads channels [0, c_in + i*width) and writes the next `width` channels:
  * ReLU(conv_{dilations[i]} + bias).  `weights` is a HOST array of `depth` device
  * pointers, weights[i] dense [width, c_in + i*width, 3, 3(, 3)]; `bias` is a device
- * pointer to depth*width values; `dilations` is a HOST array. */
+ * pointer to depth*width values; `dilations` is a HOST array.  `workspace` as for
+ * msd_conv_relu_forward (msd_forward_workspace_bytes). */
 MSD_API int msd_block_forward(int dtype, const msd_tensor_t *result, int c_in, int depth, int width,
                       const void *const *weights, const void *bias, const int *dilations,
-                      int device, void *stream);
+                      void *workspace, size_t workspace_bytes, int device, void *stream);
 
 /* Backward of all layers, last to first (msd_block.py:64-134).  `gradients` has the
  * shape of `result` and holds the gradient w.r.t. every channel on entry; it is

@@ -42,15 +42,16 @@ def _load():
         "msd_version": (i, []),
         "msd_last_error_string": (ctypes.c_char_p, []),
         "msd_workspace_bytes": (sz, [i, i, i64, i64, i64]),
-        "msd_conv_forward": (i, [i, T, vp, vp, T, i, i, vp]),
-        "msd_conv_relu_forward": (i, [i, T, vp, vp, T, i, i, vp]),
+        "msd_forward_workspace_bytes": (sz, [i, i, i64]),
+        "msd_conv_forward": (i, [i, T, vp, vp, T, i, vp, sz, i, vp]),
+        "msd_conv_relu_forward": (i, [i, T, vp, vp, T, i, vp, sz, i, vp]),
         "msd_conv_backward_x": (i, [i, T, vp, T, i, i, vp]),
         "msd_conv_relu_backward_x": (i, [i, T, T, vp, T, i, i, vp]),
         "msd_conv_backward_k": (i, [i, T, T, vp, i, vp, sz, i, vp]),
         "msd_conv_relu_backward_k": (i, [i, T, T, T, vp, i, vp, sz, i, vp]),
         "msd_conv_backward_bias": (i, [i, T, vp, vp, sz, i, vp]),
         "msd_conv_relu_backward_bias": (i, [i, T, T, vp, vp, sz, i, vp]),
-        "msd_block_forward": (i, [i, T, i, i, i, ctypes.POINTER(vp), vp, ctypes.POINTER(i), i, vp]),
+        "msd_block_forward": (i, [i, T, i, i, i, ctypes.POINTER(vp), vp, ctypes.POINTER(i), vp, sz, i, vp]),
         "msd_block_backward": (i, [i, T, T, i, i, i, ctypes.POINTER(vp), ctypes.POINTER(i), ctypes.POINTER(vp), vp, vp, sz, i, vp]),
         "msd_block_workspace_bytes": (sz, [i, i, i64, i, i, i]),
         "msd_tuning_num_variants": (i, [i]),
@@ -72,7 +73,7 @@ def _load():
 
 lib = _load()
 EXPORTED = [
-    "msd_version", "msd_last_error_string", "msd_workspace_bytes",
+    "msd_version", "msd_last_error_string", "msd_workspace_bytes", "msd_forward_workspace_bytes",
     "msd_conv_forward", "msd_conv_relu_forward", "msd_conv_backward_x", "msd_conv_relu_backward_x",
     "msd_conv_backward_k", "msd_conv_relu_backward_k", "msd_conv_backward_bias", "msd_conv_relu_backward_bias",
     "msd_block_forward", "msd_block_backward", "msd_block_workspace_bytes",

@@ -47,7 +47,7 @@ static int views2(const char *op, const msd_tensor_t *a, const msd_tensor_t *b, 
 }
 
 static int forward_impl(const char *op, bool relu, int dtype, const msd_tensor_t *input, const void *kernel, const void *bias,
-                        const msd_tensor_t *output, int d, int device, void *stream) {
+                        const msd_tensor_t *output, int d, void *ws, size_t wsb, int device, void *stream) {
     int rc = check_dtype(dtype);
     if (rc) return rc;
     View in, out;
@@ -55,11 +55,12 @@ static int forward_impl(const char *op, bool relu, int dtype, const msd_tensor_t
     if ((rc = views2(op, input, output, &in, &out, &nd))) return rc;
     if (!kernel || !bias) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: kernel and bias must not be null", op);
     if ((rc = check_dilation(op, in, nd, d))) return rc;
+    if (ws && ((uintptr_t)ws & 255)) MSD_FAIL(MSD_ERR_WORKSPACE, "%s: workspace must be 256-byte aligned", op);
     DeviceGuard g(device);
     MSD_CUDA_TRY(g.status);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == MSD_F32 && out.c == 1 && fast::forward_supported(in, out, nd, d))
-        return fast::forward(relu, in, (const float *)kernel, (const float *)bias, out, nd, d, device, s);
+    if (dtype == MSD_F32 && out.c == 1 && fast::forward_supported(in, out, nd, d, ws, wsb))
+        return fast::forward(relu, in, (const float *)kernel, (const float *)bias, out, nd, d, ws, wsb, device, s);
     return generic::forward(dtype, relu, in, kernel, bias, out, nd, d, s);
 }
 
@@ -154,14 +155,18 @@ size_t msd_workspace_bytes(int dtype, int ndim, int64_t voxels, int64_t c_in, in
     return a > b ? a : b;
 }
 
+size_t msd_forward_workspace_bytes(int dtype, int ndim, int64_t voxels) {
+    return dtype == MSD_F32 ? fast::forward_workspace_bytes(ndim == 5 ? 3 : 2, voxels) : 0;
+}
+
 int msd_conv_forward(int dtype, const msd_tensor_t *input, const void *kernel, const void *bias, const msd_tensor_t *output, int dilation,
-                     int device, void *stream) {
-    return forward_impl("conv_forward", false, dtype, input, kernel, bias, output, dilation, device, stream);
+                     void *workspace, size_t workspace_bytes, int device, void *stream) {
+    return forward_impl("conv_forward", false, dtype, input, kernel, bias, output, dilation, workspace, workspace_bytes, device, stream);
 }
 
 int msd_conv_relu_forward(int dtype, const msd_tensor_t *input, const void *kernel, const void *bias, const msd_tensor_t *output, int dilation,
-                          int device, void *stream) {
-    return forward_impl("conv_relu_forward", true, dtype, input, kernel, bias, output, dilation, device, stream);
+                          void *workspace, size_t workspace_bytes, int device, void *stream) {
+    return forward_impl("conv_relu_forward", true, dtype, input, kernel, bias, output, dilation, workspace, workspace_bytes, device, stream);
 }
 
 int msd_conv_backward_x(int dtype, const msd_tensor_t *grad_output, const void *kernel, const msd_tensor_t *grad_input, int dilation, int device,
@@ -215,12 +220,13 @@ static int block_checks(const char *op, int dtype, const msd_tensor_t *result, i
 }
 
 int msd_block_forward(int dtype, const msd_tensor_t *result, int c_in, int depth, int width, const void *const *weights, const void *bias,
-                      const int *dilations, int device, void *stream) {
+                      const int *dilations, void *workspace, size_t workspace_bytes, int device, void *stream) {
     View r;
     int nd;
     int rc = block_checks("msd_block_forward", dtype, result, c_in, depth, width, weights, dilations, &r, &nd);
     if (rc) return rc;
     if (!bias) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "msd_block_forward: bias must not be null");
+    if (workspace && ((uintptr_t)workspace & 255)) MSD_FAIL(MSD_ERR_WORKSPACE, "msd_block_forward: workspace must be 256-byte aligned");
     DeviceGuard g(device);
     MSD_CUDA_TRY(g.status);
     cudaStream_t s = (cudaStream_t)stream;
@@ -231,8 +237,8 @@ int msd_block_forward(int dtype, const msd_tensor_t *result, int c_in, int depth
         View out = channel_slice(r, n_i, width, es);
         const void *b = (const char *)bias + (size_t)i * width * es;
         const int d = dilations[i];
-        if (dtype == MSD_F32 && width == 1 && fast::forward_supported(in, out, nd, d))
-            rc = fast::forward(true, in, (const float *)weights[i], (const float *)b, out, nd, d, device, s);
+        if (dtype == MSD_F32 && width == 1 && fast::forward_supported(in, out, nd, d, workspace, workspace_bytes))
+            rc = fast::forward(true, in, (const float *)weights[i], (const float *)b, out, nd, d, workspace, workspace_bytes, device, s);
         else
             rc = generic::forward(dtype, true, in, weights[i], b, out, nd, d, s);
         if (rc) return rc;

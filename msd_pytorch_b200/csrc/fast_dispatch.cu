@@ -1,28 +1,29 @@
-// Routing of the tuned forward kernels by dimensionality.
+// Routing of the tuned forward kernels.
 #include "kernels.h"
 
 namespace msd {
 namespace fast {
 
-bool forward2d_supported(const View &in, const View &out, int d);
-int forward2d(bool relu, const View &in, const float *k, const float *bias, const View &out, int d, int device, cudaStream_t s);
+bool forward_nd_supported(const View &in, const View &out, int nd, int d, const void *ws, size_t wsb);
+int forward_nd(bool relu, const View &in, const float *k, const float *bias, const View &out, int nd, int d, void *ws, size_t wsb, int device,
+               cudaStream_t s);
 
 int num_variants(int family) {
     switch (family) {
         case FWD2D: return 3;  // lattice rows x column segments per thread
         case BWD2D: return 2;  // 4 / 8 voxels per thread
+        case FWD3D: return 2;  // 4 / 2 column segments per thread
         default: return 1;
     }
 }
 
-bool forward_supported(const View &in, const View &out, int nd, int d) {
-    if (nd == 2) return forward2d_supported(in, out, d);
-    return false;
+bool forward_supported(const View &in, const View &out, int nd, int d, const void *ws, size_t wsb) {
+    return forward_nd_supported(in, out, nd, d, ws, wsb);
 }
 
-int forward(bool relu, const View &in, const float *k, const float *bias, const View &out, int nd, int d, int device, cudaStream_t s) {
-    if (nd == 2) return forward2d(relu, in, k, bias, out, d, device, s);
-    MSD_FAIL(MSD_ERR_UNSUPPORTED, "no tuned forward kernel for this dimensionality");
+int forward(bool relu, const View &in, const float *k, const float *bias, const View &out, int nd, int d, void *ws, size_t wsb, int device,
+            cudaStream_t s) {
+    return forward_nd(relu, in, k, bias, out, nd, d, ws, wsb, device, s);
 }
 
 }  // namespace fast

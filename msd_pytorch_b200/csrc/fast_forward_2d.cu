@@ -84,42 +84,54 @@ int get_tensor_map(int device, const void *ptr, int rank, const int64_t *dims, c
 }
 
 // ---- kernel variants ----------------------------------------------------------------------
-template <int D, int R, int Q, int K>
+template <int D, int R, int Q, int K, int NT>
 static int launch_fwd2d(const CUtensorMap &map, const Fwd2dParams &p, int grid, int stages, cudaStream_t s) {
     using Cfg = Fwd2dCfg<D, R, Q, K>;
-    auto kern = forward2d_kernel<D, R, Q, K>;
-    const size_t smem = 256 + (size_t)stages * Cfg::STAGE_BYTES + (size_t)((p.C * 12 + 31) & ~31) * 4;
+    auto kern = forward2d_kernel<D, R, Q, K, NT>;
+    const size_t smem = 256 + (size_t)stages * Cfg::STAGE_BYTES + (size_t)((p.C * (NT == 3 ? 28 : 12) + 31) & ~31) * 4;
     MSD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<grid, Cfg::THREADS, smem, s>>>(map, p);
     MSD_CUDA_TRY(cudaGetLastError());
     return MSD_OK;
 }
 
-#define V(D, R, Q, K)                                                                                                       \
+#define V(D, R, Q, K, NT)                                                                                                   \
     {                                                                                                                       \
-        launch_fwd2d<D, R, Q, K>, Fwd2dCfg<D, R, Q, K>::THREADS, Fwd2dCfg<D, R, Q, K>::TH, Fwd2dCfg<D, R, Q, K>::BH,            \
+        launch_fwd2d<D, R, Q, K, NT>, Fwd2dCfg<D, R, Q, K>::THREADS, Fwd2dCfg<D, R, Q, K>::TH, Fwd2dCfg<D, R, Q, K>::BH,        \
             Fwd2dCfg<D, R, Q, K>::BW, Fwd2dCfg<D, R, Q, K>::STAGE_BYTES                                                       \
     }
-// Per dilation (index D-1): variant 0 = 4-row lattice, 4 column segments per thread;
+// 2D, per dilation (index D-1): variant 0 = 4-row lattice, 4 column segments per thread;
 // variant 1 = 4-row lattice, 2 segments (twice the warps); variant 2 = 6-row lattice, 4 segments.
 static const Fwd2dVariant kFwd2d[10][3] = {
-    {V(1, 4, 8, 4), V(1, 4, 8, 2), V(1, 6, 8, 4)},  {V(2, 4, 4, 4), V(2, 4, 4, 2), V(2, 6, 4, 4)},  {V(3, 4, 3, 4), V(3, 4, 3, 2), V(3, 6, 3, 4)},
-    {V(4, 4, 2, 4), V(4, 4, 2, 2), V(4, 6, 2, 4)},  {V(5, 4, 2, 4), V(5, 4, 2, 2), V(5, 6, 2, 4)},  {V(6, 4, 2, 4), V(6, 4, 2, 2), V(6, 6, 2, 4)},
-    {V(7, 4, 2, 4), V(7, 4, 2, 2), V(7, 6, 1, 4)},  {V(8, 4, 1, 4), V(8, 4, 1, 2), V(8, 6, 1, 4)},  {V(9, 4, 1, 4), V(9, 4, 1, 2), V(9, 6, 1, 4)},
-    {V(10, 4, 1, 4), V(10, 4, 1, 2), V(10, 6, 1, 4)},
+    {V(1, 4, 8, 4, 1), V(1, 4, 8, 2, 1), V(1, 6, 8, 4, 1)},  {V(2, 4, 4, 4, 1), V(2, 4, 4, 2, 1), V(2, 6, 4, 4, 1)},
+    {V(3, 4, 3, 4, 1), V(3, 4, 3, 2, 1), V(3, 6, 3, 4, 1)},  {V(4, 4, 2, 4, 1), V(4, 4, 2, 2, 1), V(4, 6, 2, 4, 1)},
+    {V(5, 4, 2, 4, 1), V(5, 4, 2, 2, 1), V(5, 6, 2, 4, 1)},  {V(6, 4, 2, 4, 1), V(6, 4, 2, 2, 1), V(6, 6, 2, 4, 1)},
+    {V(7, 4, 2, 4, 1), V(7, 4, 2, 2, 1), V(7, 6, 1, 4, 1)},  {V(8, 4, 1, 4, 1), V(8, 4, 1, 2, 1), V(8, 6, 1, 4, 1)},
+    {V(9, 4, 1, 4, 1), V(9, 4, 1, 2, 1), V(9, 6, 1, 4, 1)},  {V(10, 4, 1, 4, 1), V(10, 4, 1, 2, 1), V(10, 6, 1, 4, 1)},
+};
+// 3D (three z-taps per staged plane), per dilation: variant 0 = 4-row lattice, 4 column
+// segments per thread; variant 1 = 4-row lattice, 2 segments (twice the warps, shorter tiles
+// where the block would otherwise exceed ~500 threads and run out of registers).
+static const Fwd2dVariant kFwd3d[10][2] = {
+    {V(1, 4, 8, 4, 3), V(1, 4, 6, 2, 3)}, {V(2, 4, 4, 4, 3), V(2, 4, 3, 2, 3)}, {V(3, 4, 3, 4, 3), V(3, 4, 2, 2, 3)},
+    {V(4, 4, 2, 4, 3), V(4, 4, 1, 2, 3)}, {V(5, 4, 2, 4, 3), V(5, 4, 1, 2, 3)}, {V(6, 4, 2, 4, 3), V(6, 4, 1, 2, 3)},
+    {V(7, 4, 2, 4, 3), V(7, 4, 1, 2, 3)}, {V(8, 4, 1, 4, 3), V(8, 4, 1, 2, 3)}, {V(9, 4, 1, 4, 3), V(9, 4, 1, 2, 3)},
+    {V(10, 4, 1, 4, 3), V(10, 4, 1, 2, 3)},
 };
 #undef V
 
 static const size_t kFwdSmemBudget = 220 * 1024;
 
-static bool fwd2d_plan(const View &in, int d, const Fwd2dVariant **var, int *stages) {
+static bool fwd_plan(const View &in, int nd, int d, const Fwd2dVariant **var, int *stages) {
     if (d < 1 || d > 10) return false;
-    int v = tuning_get(FWD2D, d);
-    if (v < 0 || v > 2) v = 0;
-    const Fwd2dVariant *cand = &kFwd2d[d - 1][v];
-    const size_t fixed = 256 + (size_t)((in.c * 12 + 31) & ~31) * 4;
+    const int wp = nd == 3 ? 28 : 12;
+    const int nvar = nd == 3 ? 2 : 3;
+    int v = tuning_get(nd == 3 ? FWD3D : FWD2D, d);
+    if (v < 0 || v >= nvar) v = 0;
+    const Fwd2dVariant *cand = nd == 3 ? &kFwd3d[d - 1][v] : &kFwd2d[d - 1][v];
+    const size_t fixed = 256 + (size_t)((in.c * wp + 31) & ~31) * 4;
     if (fixed + 2 * (size_t)cand->stage_bytes > kFwdSmemBudget) {
-        cand = &kFwd2d[d - 1][0];
+        cand = nd == 3 ? &kFwd3d[d - 1][0] : &kFwd2d[d - 1][0];
         if (fixed + 2 * (size_t)cand->stage_bytes > kFwdSmemBudget) return false;
     }
     int s = (int)((kFwdSmemBudget - fixed) / cand->stage_bytes);
@@ -129,47 +141,78 @@ static bool fwd2d_plan(const View &in, int d, const Fwd2dVariant **var, int *sta
     return true;
 }
 
-bool forward2d_supported(const View &in, const View &out, int d) {
+size_t forward_workspace_bytes(int nd, int64_t voxels) { return nd == 3 ? (size_t)voxels * 3 * sizeof(float) + 256 : 0; }
+
+bool forward_nd_supported(const View &in, const View &out, int nd, int d, const void *ws, size_t wsb) {
     if (out.c != 1 || in.c < 1 || in.c > 4096) return false;
     if (in.sx != 1 || out.sx != 1) return false;
-    if ((in.sy % 4) || (in.sc % 4) || (in.sn % 4) || (((uintptr_t)in.p) & 15)) return false;  // TMA: 16-byte strides and base
-    if (in.x < 16 || in.x >= (1LL << 31) || in.y >= (1LL << 31)) return false;
+    // TMA: 16-byte aligned base and strides
+    if ((in.sy % 4) || (in.sz % 4) || (in.sc % 4) || (in.sn % 4) || (((uintptr_t)in.p) & 15)) return false;
+    if (in.x < 16 || in.x >= (1LL << 31) || in.y >= (1LL << 31) || in.z >= (1LL << 31)) return false;
     if (in.sy < in.x) return false;
+    if (nd == 3) {
+        // the z-gather kernel writes 128-bit vectors and needs the scratch planes
+        if ((in.x % 4) || (out.sy % 4) || (out.sz % 4) || (out.sn % 4) || (((uintptr_t)out.p) & 15)) return false;
+        if (!ws || wsb < forward_workspace_bytes(3, in.n * in.z * in.y * in.x)) return false;
+    }
     const Fwd2dVariant *var;
     int stages;
-    return fwd2d_plan(in, d, &var, &stages);
+    return fwd_plan(in, nd, d, &var, &stages);
 }
 
-int forward2d(bool relu, const View &in, const float *k, const float *bias, const View &out, int d, int device, cudaStream_t s) {
+int forward_nd(bool relu, const View &in, const float *k, const float *bias, const View &out, int nd, int d, void *ws, size_t wsb, int device,
+               cudaStream_t s) {
     const Fwd2dVariant *var;
     int stages;
-    if (!fwd2d_plan(in, d, &var, &stages)) MSD_FAIL(MSD_ERR_UNSUPPORTED, "forward2d: shape not supported");
-    // The descriptor spans every channel that lies behind the view's base pointer in the
-    // same allocation pattern; only channels [0, C) are ever addressed.
-    const int64_t dims[4] = {in.x, in.y, in.c, in.n};
-    const int64_t strides[4] = {1, in.sy, in.sc, in.sn};
-    const int box[4] = {var->bw, var->bh, 1, 1};
+    if (!fwd_plan(in, nd, d, &var, &stages)) MSD_FAIL(MSD_ERR_UNSUPPORTED, "forward: shape not supported");
     CUtensorMap map;
-    int rc = get_tensor_map(device, in.p, 4, dims, strides, box, &map);
+    int rc;
+    if (nd == 3) {
+        const int64_t dims[5] = {in.x, in.y, in.z, in.c, in.n};
+        const int64_t strides[5] = {1, in.sy, in.sz, in.sc, in.sn};
+        const int box[5] = {var->bw, var->bh, 1, 1, 1};
+        rc = get_tensor_map(device, in.p, 5, dims, strides, box, &map);
+    } else {
+        const int64_t dims[4] = {in.x, in.y, in.c, in.n};
+        const int64_t strides[4] = {1, in.sy, in.sc, in.sn};
+        const int box[4] = {var->bw, var->bh, 1, 1};
+        rc = get_tensor_map(device, in.p, 4, dims, strides, box, &map);
+    }
     if (rc) return rc;
     Fwd2dParams p;
     memset(&p, 0, sizeof(p));
-    p.out = (float *)out.p;
-    p.out_sn = out.sn, p.out_sy = out.sy;
+    const int64_t vox = in.n * in.z * in.y * in.x;
+    if (nd == 3) {
+        p.out = (float *)ws;  // u[3][N][Z][Y][X]
+        p.out_st = vox, p.out_sn = in.z * in.y * in.x, p.out_sz = in.y * in.x, p.out_sy = in.x;
+    } else {
+        p.out = (float *)out.p;
+        p.out_st = 0, p.out_sn = out.sn, p.out_sz = 0, p.out_sy = out.sy;
+    }
     p.k = k, p.bias = bias;
-    p.N = (int)in.n, p.C = (int)in.c, p.Y = (int)in.y, p.X = (int)in.x;
+    p.N = (int)in.n, p.C = (int)in.c, p.Z = (int)in.z, p.Y = (int)in.y, p.X = (int)in.x;
     p.tiles_x = (int)ceil_div(in.x, kFwdTW);
     p.tiles_y = (int)ceil_div(in.y, var->th);
-    p.num_tiles = (long long)p.tiles_x * p.tiles_y * in.n;
+    p.num_tiles = (long long)p.tiles_x * p.tiles_y * in.z * in.n;
     p.stages = stages;
     p.relu = relu ? 1 : 0;
     p.status = tma::device_status_ptr(device);
-    if (!p.status) MSD_FAIL(MSD_ERR_CUDA, "forward2d: cannot locate the device status word");
+    if (!p.status) MSD_FAIL(MSD_ERR_CUDA, "forward: cannot locate the device status word");
     int grid = sm_count(device);
     if (p.num_tiles < grid) grid = (int)p.num_tiles;
     rc = var->launch(map, p, grid, stages, s);
     if (rc) return rc;
     count_launch(true);
+    if (nd == 3) {
+        const int64_t quads = vox / 4;
+        int64_t g = ceil_div(quads, 256);
+        const int64_t gmax = (int64_t)sm_count(device) * 16;
+        if (g > gmax) g = gmax;
+        zgather_kernel<<<(unsigned)g, 256, 0, s>>>((const float *)ws, (float *)out.p, out.sn, out.sz, out.sy, bias, (int)in.n, (int)in.z, (int)in.y,
+                                                   (int)in.x, d, relu ? 1 : 0);
+        count_launch(true);
+        MSD_CUDA_TRY(cudaGetLastError());
+    }
     return MSD_OK;
 }
 

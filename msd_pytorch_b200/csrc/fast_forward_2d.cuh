@@ -21,6 +21,14 @@
 // touch the left or right image border the x-D tap of the first segment and the x+D taps
 // use per-thread offsets that point at the mirror cell (always inside the same box); all
 // other tiles run a copy of the loop with compile-time offsets.
+//
+// 3D layers (NT = 3) run the same kernel once per z-plane: from one staged 2D tile of
+// in[c][z'] a thread accumulates the three in-plane 3x3 sums u_tz[z'] (one per z-tap, 27
+// FMAs per loaded lattice value triple), written to a scratch buffer; a second, purely
+// streaming kernel then forms out[z] = [relu](bias + u_0[refl(z-D)] + u_1[z] + u_2[refl(z+D)])
+// (conv3d_forward.cu:110-196 of the reference, sum re-associated by z-tap).  This keeps the
+// staged tiles two-dimensional (a three-dimensional halo for D = 10 does not fit in shared
+// memory) and raises the FMA : shared-load ratio to 6.
 #pragma once
 #include "common.cuh"
 #include "kernels.h"
@@ -33,11 +41,11 @@ constexpr int kFwdTW = 128;  // tile width
 constexpr int kFwdMaxStages = 8;
 
 struct Fwd2dParams {
-    float *out;
-    int64_t out_sn, out_sy;
-    const float *k;     // [C][9]
+    float *out;          // NT == 1: the output channel; NT == 3: scratch u[3][N][Z][Y][X]
+    int64_t out_st, out_sn, out_sz, out_sy;
+    const float *k;     // [C][NT*9]
     const float *bias;  // [1]
-    int N, C, Y, X;
+    int N, C, Z, Y, X;
     int tiles_x, tiles_y;
     long long num_tiles;
     int stages;
@@ -58,15 +66,20 @@ struct Fwd2dCfg {
     static constexpr int STAGE = STAGE_BYTES / 4;
 };
 
-// One input channel's contribution to a thread's R x K accumulators.  `rp[m]` points at the
-// thread's first column in lattice row m of the box; BORDER selects run-time column
-// offsets for the taps that may leave the image.
-template <int D, int R, int K, bool BORDER>
-__device__ __forceinline__ void fwd2d_channel(float (&acc)[R][K], const float *st, const int (&rowoff)[R + 2], const float *wsm_c, int dl,
+// One input channel's contribution to a thread's NT x R x K accumulators.  `rowoff[m]` is the
+// offset of the thread's first column in lattice row m of the box; BORDER selects run-time
+// column offsets for the taps that may leave the image.
+template <int D, int R, int K, int NT, bool BORDER>
+__device__ __forceinline__ void fwd2d_channel(float (&acc)[NT][R][K], const float *st, const int (&rowoff)[R + 2], const float *wsm_c, int dl,
                                               const int (&dr)[K]) {
+    constexpr int WP = (NT == 3) ? 28 : 12;
+    float w[WP];
     const float4 *wp = reinterpret_cast<const float4 *>(wsm_c);
-    const float4 w0 = wp[0], w1 = wp[1], w2 = wp[2];
-    const float w[9] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w, w2.x};
+#pragma unroll
+    for (int i = 0; i < WP / 4; ++i) {
+        const float4 t4 = wp[i];
+        w[4 * i + 0] = t4.x, w[4 * i + 1] = t4.y, w[4 * i + 2] = t4.z, w[4 * i + 3] = t4.w;
+    }
 #pragma unroll
     for (int m = 0; m < R + 2; ++m) {
         const float *rp = st + rowoff[m];
@@ -79,18 +92,22 @@ __device__ __forceinline__ void fwd2d_channel(float (&acc)[R][K], const float *s
             for (int j = 0; j < R; ++j) {
                 const int t = m - j;  // tap row of output row j that reads lattice row m
                 if (t >= 0 && t <= 2) {
-                    acc[j][k] = fmaf(w[t * 3 + 0], a, acc[j][k]);
-                    acc[j][k] = fmaf(w[t * 3 + 1], b, acc[j][k]);
-                    acc[j][k] = fmaf(w[t * 3 + 2], cc, acc[j][k]);
+#pragma unroll
+                    for (int tz = 0; tz < NT; ++tz) {
+                        acc[tz][j][k] = fmaf(w[tz * 9 + t * 3 + 0], a, acc[tz][j][k]);
+                        acc[tz][j][k] = fmaf(w[tz * 9 + t * 3 + 1], b, acc[tz][j][k]);
+                        acc[tz][j][k] = fmaf(w[tz * 9 + t * 3 + 2], cc, acc[tz][j][k]);
+                    }
                 }
             }
         }
     }
 }
 
-template <int D, int R, int Q, int K>
+template <int D, int R, int Q, int K, int NT>
 __global__ void __launch_bounds__(Fwd2dCfg<D, R, Q, K>::THREADS, 1)
 forward2d_kernel(const __grid_constant__ CUtensorMap map, const Fwd2dParams p) {
+    constexpr int WP = (NT == 3) ? 28 : 12;  // weights per channel, padded to whole float4s
     using Cfg = Fwd2dCfg<D, R, Q, K>;
     constexpr int NCW = Cfg::NCW, XW = Cfg::XW, TH = Cfg::TH, DP = Cfg::DP, BW = Cfg::BW, BH = Cfg::BH, STAGE = Cfg::STAGE;
     constexpr int TW = kFwdTW;
@@ -99,7 +116,7 @@ forward2d_kernel(const __grid_constant__ CUtensorMap map, const Fwd2dParams p) {
     uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw);
     uint64_t *empty = full + kFwdMaxStages;
     volatile int *abort_flag = reinterpret_cast<volatile int *>(empty + kFwdMaxStages);
-    const int wfloats = (p.C * 12 + 31) & ~31;
+    const int wfloats = (p.C * WP + 31) & ~31;
     float *ring = reinterpret_cast<float *>(smem_raw + 256);
     float *wsm = ring + (size_t)p.stages * STAGE;
 
@@ -115,8 +132,8 @@ forward2d_kernel(const __grid_constant__ CUtensorMap map, const Fwd2dParams p) {
         tma::prefetch_tensormap(&map);
     }
     for (int i = tid; i < wfloats; i += Cfg::THREADS) {
-        const int c = i / 12, t = i % 12;
-        wsm[i] = (c < p.C && t < 9) ? p.k[c * 9 + t] : 0.f;
+        const int c = i / WP, t = i % WP;
+        wsm[i] = (c < p.C && t < NT * 9) ? p.k[c * NT * 9 + t] : 0.f;
     }
     __syncthreads();
 
@@ -129,13 +146,17 @@ forward2d_kernel(const __grid_constant__ CUtensorMap map, const Fwd2dParams p) {
             for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
                 const int tx_i = (int)(tile % p.tiles_x);
                 const int ty_i = (int)((tile / p.tiles_x) % p.tiles_y);
-                const int n = (int)(tile / tiles_per_image);
+                const long long nz = tile / tiles_per_image;
+                const int z = (int)(nz % p.Z), n = (int)(nz / p.Z);
                 const int bx = tx_i * TW - DP, by = ty_i * TH - D;
                 for (int c = 0; c < p.C; ++c, ++it) {
                     const int s = it % S;
                     if (it >= (uint32_t)S) tma::wait_parity(&empty[s], ((it / S) & 1u) ^ 1u, abort_flag, p.status, 3);
                     tma::mbar_arrive_expect_tx(&full[s], BH * BW * 4);
-                    tma::tensor_g2s_4d(ring + (size_t)s * STAGE, &map, bx, by, c, n, &full[s]);
+                    if (NT == 3)
+                        tma::tensor_g2s_5d(ring + (size_t)s * STAGE, &map, bx, by, z, c, n, &full[s]);
+                    else
+                        tma::tensor_g2s_4d(ring + (size_t)s * STAGE, &map, bx, by, c, n, &full[s]);
                 }
             }
         }
@@ -151,7 +172,8 @@ forward2d_kernel(const __grid_constant__ CUtensorMap map, const Fwd2dParams p) {
     for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
         const int tx_i = (int)(tile % p.tiles_x);
         const int ty_i = (int)((tile / p.tiles_x) % p.tiles_y);
-        const int n = (int)(tile / tiles_per_image);
+        const long long nz = tile / tiles_per_image;
+        const int z = (int)(nz % p.Z), n = (int)(nz / p.Z);
         const int x0 = tx_i * TW, y0 = ty_i * TH;
 
         // Shared-memory offset of each lattice row (reflected at the top/bottom border and
@@ -176,40 +198,80 @@ forward2d_kernel(const __grid_constant__ CUtensorMap map, const Fwd2dParams p) {
             dr[k] = (x < p.X && x + D >= p.X) ? 2 * p.X - 1 - 2 * x - D : D;  // x + D >= X mirrors to 2X - 1 - (x + D)
         }
 
-        float acc[R][K];
+        float acc[NT][R][K];
 #pragma unroll
-        for (int j = 0; j < R; ++j)
+        for (int tz = 0; tz < NT; ++tz)
 #pragma unroll
-            for (int k = 0; k < K; ++k) acc[j][k] = bias;
+            for (int j = 0; j < R; ++j)
+#pragma unroll
+                for (int k = 0; k < K; ++k) acc[tz][j][k] = (NT == 1) ? bias : 0.f;
 
         for (int c = 0; c < p.C; ++c, ++it) {
             const int s = it % S;
             tma::wait_parity(&full[s], (it / S) & 1u, abort_flag, p.status, 4);
             const float *st = ring + (size_t)s * STAGE;
             if (border)
-                fwd2d_channel<D, R, K, true>(acc, st, rowoff, wsm + c * 12, dl, dr);
+                fwd2d_channel<D, R, K, NT, true>(acc, st, rowoff, wsm + c * WP, dl, dr);
             else
-                fwd2d_channel<D, R, K, false>(acc, st, rowoff, wsm + c * 12, dl, dr);
+                fwd2d_channel<D, R, K, NT, false>(acc, st, rowoff, wsm + c * WP, dl, dr);
             __syncwarp();
             if (lane == 0) tma::mbar_arrive(&empty[s]);
         }
 
         if (!*abort_flag) {
-            float *ob = p.out + n * p.out_sn;
 #pragma unroll
-            for (int j = 0; j < R; ++j) {
-                const int y = y0 + q * R * D + i + j * D;
-                if (y < p.Y) {
+            for (int tz = 0; tz < NT; ++tz) {
+                float *ob = p.out + tz * p.out_st + n * p.out_sn + z * p.out_sz;
 #pragma unroll
-                    for (int k = 0; k < K; ++k) {
-                        const int x = x0 + cb + 32 * k;
-                        float v = acc[j][k];
-                        if (p.relu) v = v > 0.f ? v : 0.f;
-                        if (x < p.X) ob[(int64_t)y * p.out_sy + x] = v;
+                for (int j = 0; j < R; ++j) {
+                    const int y = y0 + q * R * D + i + j * D;
+                    if (y < p.Y) {
+#pragma unroll
+                        for (int k = 0; k < K; ++k) {
+                            const int x = x0 + cb + 32 * k;
+                            float v = acc[tz][j][k];
+                            if (NT == 1 && p.relu) v = v > 0.f ? v : 0.f;
+                            if (x < p.X) ob[(int64_t)y * p.out_sy + x] = v;
+                        }
                     }
                 }
             }
         }
+    }
+}
+
+// Second kernel of the 3D forward: out[n][z][y][x] = [relu](bias + u0[refl(z-d)] + u1[z] + u2[refl(z+d)]),
+// u dense [3][N][Z][Y][X], four voxels per thread.
+__global__ void __launch_bounds__(256)
+zgather_kernel(const float *__restrict__ u, float *__restrict__ out, int64_t out_sn, int64_t out_sz, int64_t out_sy, const float *__restrict__ bias,
+               int N, int Z, int Y, int X, int d, int relu) {
+    const int xq = X / 4;
+    const int64_t total = (int64_t)N * Z * Y * xq;
+    const int64_t plane = (int64_t)Y * X, vol = plane * Z, ust = vol * N;
+    const float b = bias[0];
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int x4 = (int)(i % xq);
+        int64_t r = i / xq;
+        const int y = (int)(r % Y);
+        r /= Y;
+        const int z = (int)(r % Z), n = (int)(r / Z);
+        const int zm = reflect(z - d, Z), zp = reflect(z + d, Z);
+        const int64_t off = (int64_t)n * vol + (int64_t)y * X + 4 * x4;
+        const float4 a0 = *reinterpret_cast<const float4 *>(u + off + zm * plane);
+        const float4 a1 = *reinterpret_cast<const float4 *>(u + ust + off + z * plane);
+        const float4 a2 = *reinterpret_cast<const float4 *>(u + 2 * ust + off + zp * plane);
+        float4 v;
+        v.x = b + a0.x + a1.x + a2.x;
+        v.y = b + a0.y + a1.y + a2.y;
+        v.z = b + a0.z + a1.z + a2.z;
+        v.w = b + a0.w + a1.w + a2.w;
+        if (relu) {
+            v.x = v.x > 0.f ? v.x : 0.f;
+            v.y = v.y > 0.f ? v.y : 0.f;
+            v.z = v.z > 0.f ? v.z : 0.f;
+            v.w = v.w > 0.f ? v.w : 0.f;
+        }
+        *reinterpret_cast<float4 *>(out + n * out_sn + z * out_sz + (int64_t)y * out_sy + 4 * x4) = v;
     }
 }
 

@@ -24,14 +24,12 @@ int tuning_set(int family, int dilation, int variant);
 int tuning_get(int family, int dilation);
 
 // Forward: out = [relu](bias + conv_d(in)), in has C channels, out has 1.
-bool forward_supported(const View &in, const View &out, int nd, int d);
-int forward(bool relu, const View &in, const float *k, const float *bias, const View &out, int nd, int d, int device, cudaStream_t s);
+// `ws` is scratch for the 3D forward (three partial-sum volumes); 2D needs none.
+size_t forward_workspace_bytes(int nd, int64_t voxels);
+bool forward_supported(const View &in, const View &out, int nd, int d, const void *ws, size_t wsb);
+int forward(bool relu, const View &in, const float *k, const float *bias, const View &out, int nd, int d, void *ws, size_t wsb, int device,
+            cudaStream_t s);
 
-// Fused backward of one layer.  m = gout * gate(out); for every input channel c:
-//   gin[c] += conv_d^T(m, k[c])        (if gin)
-//   gk[c,:] += <in[c] shifted, m>      (if gk; deterministic two-pass)
-//   gb      += sum m                   (if gb)
-// `out` may be null (no gate).  `in` may be null when gk is null.
 // Deferred second pass of the weight/bias gradient reduction: the fused backward of every
 // layer of a block appends one entry, and one table-driven kernel adds all partials at the end.
 struct ReduceEntry {
@@ -49,6 +47,11 @@ struct ReduceList {
 };
 int flush_reductions(ReduceList *list, cudaStream_t s);
 
+// Fused backward of one layer.  m = gout * gate(out); for every input channel c:
+//   gin[c] += conv_d^T(m, k[c])        (if gin)
+//   gk[c,:] += <in[c] shifted, m>      (if gk; deterministic two-pass)
+//   gb      += sum m                   (if gb)
+// `out` may be null (no gate).  `in` may be null when gk is null.
 struct BackwardArgs {
     const View *out;   // [N,1,...] ReLU output (gate) or null
     const View *gout;  // [N,1,...]

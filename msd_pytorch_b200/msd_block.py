@@ -47,8 +47,13 @@ def block_forward_(result, c_in, dilations, bias, weights):
     dt = _lib.dtype_code(result.dtype)
     width = _uniform_width(weights)
     if width is not None:
+        need = _lib.lib.msd_forward_workspace_bytes(dt, result.dim(), _voxels(result))
+        ws_ptr, ws_len = None, 0
+        if need:
+            ws = _lib.workspace(dev, need)
+            ws_ptr, ws_len = ws.data_ptr(), ws.numel()
         _lib.check(_lib.lib.msd_block_forward(dt, _lib.describe(result), c_in, len(weights), width, _pointer_array(weights), bias.data_ptr(),
-                                              _int_array(dilations), dev.index, _lib.stream_of(dev)))
+                                              _int_array(dilations), ws_ptr, ws_len, dev.index, _lib.stream_of(dev)))
         return
     start, bstart = c_in, 0
     for w, d in zip(weights, dilations):

@@ -104,7 +104,16 @@ def _forward(c, relu, input, kernel, bias, output, dilation):
     _bias_checks(c, bias, output.shape[1])
     d = _dilation(c, input, dilation)
     fn = _lib_.msd_conv_relu_forward if relu else _lib_.msd_conv_forward
-    _lib.check(fn(dt, _lib.describe(input), kernel.data_ptr(), bias.data_ptr(), _lib.describe(output), d, dev.index, _lib.stream_of(dev)))
+    voxels = input.shape[0]
+    for s in input.shape[2:]:
+        voxels *= s
+    need = _lib_.msd_forward_workspace_bytes(dt, input.dim(), voxels)
+    ws_ptr, ws_len = None, 0
+    if need:
+        buf = _lib.workspace(dev, need)
+        ws_ptr, ws_len = buf.data_ptr(), buf.numel()
+    _lib.check(fn(dt, _lib.describe(input), kernel.data_ptr(), bias.data_ptr(), _lib.describe(output), d, ws_ptr, ws_len, dev.index,
+                  _lib.stream_of(dev)))
 
 
 def conv_forward(input, kernel, bias, output, dilation, block_size=None):

@@ -68,21 +68,22 @@ def test_c_abi_argument_errors_need_no_gpu():
     L = _lib.lib
     a, b = _desc((1, 2, 4, 4)), _desc((1, 1, 4, 4))
     # dilation 0 and dilation > size  (msd_custom_convolutions.cpp:39-52)
-    assert L.msd_conv_forward(0, a, 256, 256, b, 0, 0, None) == 1
+    assert L.msd_conv_forward(0, a, 256, 256, b, 0, None, 0, 0, None) == 1
     assert b"Dilation must be 1 or greater" in L.msd_last_error_string()
-    assert L.msd_conv_forward(0, a, 256, 256, b, 5, 0, None) == 1
+    assert L.msd_conv_forward(0, a, 256, 256, b, 5, None, 0, 0, None) == 1
     assert b"Dilation cannot be greater" in L.msd_last_error_string()
     # shape mismatch (msd_custom_convolutions.cpp:69-83)
-    assert L.msd_conv_relu_forward(0, a, 256, 256, _desc((1, 1, 4, 5)), 1, 0, None) == 1
-    assert L.msd_conv_relu_forward(0, a, 256, 256, _desc((2, 1, 4, 4)), 1, 0, None) == 1
+    assert L.msd_conv_relu_forward(0, a, 256, 256, _desc((1, 1, 4, 5)), 1, None, 0, 0, None) == 1
+    assert L.msd_conv_relu_forward(0, a, 256, 256, _desc((2, 1, 4, 4)), 1, None, 0, 0, None) == 1
     # rank mismatch, bad dtype, null pointers
-    assert L.msd_conv_forward(0, a, 256, 256, _desc((1, 1, 1, 4, 4)), 1, 0, None) == 1
-    assert L.msd_conv_forward(7, a, 256, 256, b, 1, 0, None) == 2
-    assert L.msd_conv_forward(0, a, None, 256, b, 1, 0, None) == 1
+    assert L.msd_conv_forward(0, a, 256, 256, _desc((1, 1, 1, 4, 4)), 1, None, 0, 0, None) == 1
+    assert L.msd_conv_forward(7, a, 256, 256, b, 1, None, 0, 0, None) == 2
+    assert L.msd_conv_forward(0, a, None, 256, b, 1, None, 0, 0, None) == 1
+    assert L.msd_forward_workspace_bytes(0, 5, 1000) >= 12000 and L.msd_forward_workspace_bytes(0, 4, 1000) == 0
     # misaligned workspace
     assert L.msd_conv_backward_k(0, b, a, 256, 1, 13, 1 << 20, 0, None) == 3
     # block: channel count must be c_in + depth*width
     ptrs = (ctypes.c_void_p * 2)(256, 256)
     dil = (ctypes.c_int * 2)(1, 1)
-    assert L.msd_block_forward(0, _desc((1, 4, 4, 4)), 1, 2, 1, ptrs, 256, dil, 0, None) == 1
+    assert L.msd_block_forward(0, _desc((1, 4, 4, 4)), 1, 2, 1, ptrs, 256, dil, None, 0, 0, None) == 1
     assert L.msd_workspace_bytes(0, 4, 1 << 20, 100, 1) > 0

@@ -67,7 +67,7 @@ def test_2d_every_dilation(cc, cuda_device, d):
 
 @pytest.mark.parametrize("d", [1, 2, 3, 4, 5, 6, 7, 8, 9, 10])
 def test_3d_every_dilation(cc, cuda_device, d):
-    check_layer(cc, cuda_device, 1, 3, (12, 20, 136), d, seed=100 + d, expect_fast=2)
+    check_layer(cc, cuda_device, 1, 3, (12, 20, 136), d, seed=100 + d, expect_fast=4)
 
 
 @pytest.mark.parametrize("sp,d", [((16, 16), 16), ((10, 16), 10), ((33, 64), 7), ((5, 260), 5), ((130, 20), 3), ((512, 512), 10)])
@@ -77,18 +77,18 @@ def test_2d_edges(cc, cuda_device, sp, d):
 
 @pytest.mark.parametrize("sp,d", [((10, 10, 16), 10), ((3, 40, 24), 3), ((9, 5, 132), 4), ((32, 32, 64), 6)])
 def test_3d_edges(cc, cuda_device, sp, d):
-    check_layer(cc, cuda_device, 2, 2, sp, d, seed=8, expect_fast=2)
+    check_layer(cc, cuda_device, 2, 2, sp, d, seed=8, expect_fast=4)
 
 
 def test_many_tiles_per_block_and_many_channels(cc, cuda_device):
     """More tiles than thread blocks (persistent round-robin) and a deep channel loop."""
     check_layer(cc, cuda_device, 4, 40, (256, 512), 9, seed=11)
-    check_layer(cc, cuda_device, 2, 20, (40, 48, 128), 5, seed=12, expect_fast=2)
+    check_layer(cc, cuda_device, 2, 20, (40, 48, 128), 5, seed=12, expect_fast=4)
 
 
 def test_linear_variants(cc, cuda_device):
     check_layer(cc, cuda_device, 2, 4, (48, 160), 3, relu=False, seed=13)
-    check_layer(cc, cuda_device, 1, 4, (8, 24, 64), 2, relu=False, seed=14, expect_fast=2)
+    check_layer(cc, cuda_device, 1, 4, (8, 24, 64), 2, relu=False, seed=14, expect_fast=4)
 
 
 @pytest.mark.parametrize("nd", [2, 3])
@@ -157,3 +157,28 @@ def test_forward_launch_variants(cc, cuda_device, d, variant):
         assert_close(y, y_o, 1e-4, "forward variant %d" % variant)
     finally:
         _lib.lib.msd_tuning_set(_lib.FAMILY_FWD2D, d, -1)
+
+
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("d", [1, 2, 3, 4, 5, 6, 7, 8, 9, 10])
+def test_forward3d_launch_variants(cc, cuda_device, d, variant):
+    """Both variants of the 3D forward (plane-wise TMA kernel + z-gather) match the oracle on a
+    volume with ragged tiles in y and x and every z-plane near a border for large dilations."""
+    from msd_pytorch_b200 import _lib
+    from oracle import msd_oracle as O
+
+    dev = cuda_device
+    assert _lib.lib.msd_tuning_num_variants(_lib.FAMILY_FWD3D) == 2
+    _lib.check(_lib.lib.msd_tuning_set(_lib.FAMILY_FWD3D, d, variant))
+    try:
+        x, k, b, go = util.make_op_inputs(2, 3, 1, (11, 50, 140), torch.float32, 70 + d, dev)
+        y = torch.empty_like(go, device=dev)
+        before = _counts()
+        cc.conv_relu_forward(x.to(dev), k.to(dev), b.to(dev), y, d)
+        assert _status(dev) == 0
+        assert _counts()[1] - before[1] == 2
+        y_o = torch.empty_like(go, dtype=torch.float64)
+        O.conv_relu_forward(x.double(), k.double(), b.double(), y_o, d)
+        assert_close(y, y_o, 1e-4, "forward3d variant %d" % variant)
+    finally:
+        _lib.lib.msd_tuning_set(_lib.FAMILY_FWD3D, d, -1)
