@@ -433,7 +433,7 @@ def main():
     if args.config == "c5":
         from msd_pytorch_b200 import slab_bench
 
-        slab_bench.main(args, cfg, rank, world, local)
+        slab_bench.main(args, cfg, rank, world, local, peak=measured_peak())
         return
 
     if not torch.cuda.is_available():

@@ -152,6 +152,29 @@ MSD_API int msd_block_backward(int dtype, const msd_tensor_t *result, const msd_
 /* Scratch bytes `msd_block_backward` needs. */
 MSD_API size_t msd_block_workspace_bytes(int dtype, int ndim, int64_t voxels, int c_in, int depth, int width);
 
+/* ---- z-slab decomposition of one 3D volume over several GPUs ---- */
+
+/* No counterpart in the reference (it has no spatial decomposition).  One layer of the
+ * block on a z-slab: `buffer[N, C, Zl, Y, X]` (float32) is this GPU's part of the dense
+ * buffer, its planes [z_begin, z_end) owned, the planes below/above them halo copies of
+ * the neighbours' planes (at least `dilation` of them, except at the volume's real ends,
+ * where the buffer ends too and the edge-inclusive reflection applies).  Reads channels
+ * [0, n_in) on owned + halo planes, writes channel n_in on the owned planes only.  The
+ * caller exchanges that channel's boundary planes afterwards.  Needs the workspace of
+ * msd_forward_workspace_bytes() for the whole local buffer. */
+MSD_API int msd_slab_layer_forward(const msd_tensor_t *buffer, int n_in, const void *weight, const void *bias,
+                           int dilation, int z_begin, int z_end, void *workspace, size_t workspace_bytes,
+                           int device, void *stream);
+
+/* Backward of the same layer on the slab: uses channel n_in of `result` (gate) and of
+ * `gradients` on owned + halo planes (the caller has exchanged the gradient halo), adds the
+ * input gradient into channels [0, n_in) of `gradients` on the owned planes, and this
+ * slab's share of the weight / bias gradient into grad_weight / grad_bias (either may be
+ * NULL); the caller sums those over the GPUs. */
+MSD_API int msd_slab_layer_backward(const msd_tensor_t *result, const msd_tensor_t *gradients, int n_in,
+                            const void *weight, int dilation, int z_begin, int z_end, void *grad_weight,
+                            void *grad_bias, void *workspace, size_t workspace_bytes, int device, void *stream);
+
 /* ---- launch autotuner (replaces benchmarks/benchmark_block_sizes.py) ---- */
 
 /* Number of launch variants the library has for a kernel family

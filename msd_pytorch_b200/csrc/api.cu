@@ -299,6 +299,55 @@ int msd_block_backward(int dtype, const msd_tensor_t *result, const msd_tensor_t
     return fast::flush_reductions(&pending, s);
 }
 
+// One layer of a block on a z-slab: same kernels as the block entry points, restricted to the
+// planes [z_begin, z_end) of the local buffer; the planes outside are halo (read only).
+static int slab_checks(const char *op, const msd_tensor_t *buffer, int n_in, int dilation, int z_begin, int z_end, View *r) {
+    if (!make_view(buffer, r) || buffer->ndim != 5) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: buffer must be 5-dimensional (N, C, Z, Y, X)", op);
+    if (n_in < 1 || n_in >= r->c) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: n_in = %d must lie in [1, channels)", op, n_in);
+    if (z_begin < 0 || z_end > r->z || z_begin >= z_end) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "%s: bad z window [%d, %d) for %lld planes", op, z_begin, z_end, (long long)r->z);
+    return check_dilation(op, *r, 3, dilation);
+}
+
+int msd_slab_layer_forward(const msd_tensor_t *buffer, int n_in, const void *weight, const void *bias, int dilation, int z_begin, int z_end,
+                           void *workspace, size_t workspace_bytes, int device, void *stream) {
+    View r;
+    int rc = slab_checks("msd_slab_layer_forward", buffer, n_in, dilation, z_begin, z_end, &r);
+    if (rc) return rc;
+    if (!weight || !bias) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "msd_slab_layer_forward: weight and bias must not be null");
+    DeviceGuard g(device);
+    MSD_CUDA_TRY(g.status);
+    View in = channel_slice(r, 0, n_in, 4), out = channel_slice(r, n_in, 1, 4);
+    if (!fast::forward_supported(in, out, 3, dilation, workspace, workspace_bytes))
+        MSD_FAIL(MSD_ERR_UNSUPPORTED, "msd_slab_layer_forward: shape, alignment, dilation (1..10) or workspace not supported by the tuned 3D kernel");
+    fast::set_z_window(z_begin, z_end);
+    rc = fast::forward(true, in, (const float *)weight, (const float *)bias, out, 3, dilation, workspace, workspace_bytes, device, (cudaStream_t)stream);
+    fast::set_z_window(0, 0);
+    return rc;
+}
+
+int msd_slab_layer_backward(const msd_tensor_t *result, const msd_tensor_t *gradients, int n_in, const void *weight, int dilation, int z_begin,
+                            int z_end, void *grad_weight, void *grad_bias, void *workspace, size_t workspace_bytes, int device, void *stream) {
+    View r, gr;
+    int rc = slab_checks("msd_slab_layer_backward", result, n_in, dilation, z_begin, z_end, &r);
+    if (rc) return rc;
+    int nd;
+    if ((rc = views2("msd_slab_layer_backward", result, gradients, &r, &gr, &nd))) return rc;
+    if (gr.c != r.c) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "msd_slab_layer_backward: gradients and result differ in channels");
+    if (!weight) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "msd_slab_layer_backward: weight must not be null");
+    if (workspace && ((uintptr_t)workspace & 255)) MSD_FAIL(MSD_ERR_WORKSPACE, "msd_slab_layer_backward: workspace must be 256-byte aligned");
+    DeviceGuard g(device);
+    MSD_CUDA_TRY(g.status);
+    View out = channel_slice(r, n_in, 1, 4), in = channel_slice(r, 0, n_in, 4);
+    View gout = channel_slice(gr, n_in, 1, 4), gin = channel_slice(gr, 0, n_in, 4);
+    fast::BackwardArgs a{&out, &gout, &in, &gin, (const float *)weight, (float *)grad_weight, (float *)grad_bias, 3, dilation, workspace, workspace_bytes, nullptr};
+    if (!fast::backward_supported(a))
+        MSD_FAIL(MSD_ERR_UNSUPPORTED, "msd_slab_layer_backward: shape, alignment, dilation or workspace not supported by the tuned 3D kernel");
+    fast::set_z_window(z_begin, z_end);
+    rc = fast::backward(a, device, (cudaStream_t)stream);
+    fast::set_z_window(0, 0);
+    return rc;
+}
+
 int msd_tuning_num_variants(int family) { return fast::num_variants(family); }
 int msd_tuning_set(int family, int dilation, int variant) { return fast::tuning_set(family, dilation, variant); }
 int msd_tuning_get(int family, int dilation) { return fast::tuning_get(family, dilation); }

@@ -68,6 +68,7 @@ struct BwdParams {
     float *part_k;   // [grid][C*TAPS]
     float *part_b;   // [grid] or null
     int N, C, Z, Y, X;
+    int z0, ZW;  // planes [z0, z0 + ZW) are processed (the whole volume unless a z-slab window is set)
     int d, Dp;  // dilation and dilation rounded up to a multiple of 4
     int tiles_x, tiles_y;
     long long num_tiles;
@@ -199,7 +200,7 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
                 const int tx_i = (int)(tile % p.tiles_x);
                 const int ty_i = (int)((tile / p.tiles_x) % p.tiles_y);
                 const long long nz = tile / tiles_per_plane;
-                const int z = (int)(nz % p.Z), n = (int)(nz / p.Z);
+                const int z = p.z0 + (int)(nz % p.ZW), n = (int)(nz / p.ZW);
                 const int bx = tx_i * TX - p.Dp, y0 = ty_i * TR;
                 tma::mbar_arrive_expect_tx(halo_full, halo_bytes);
 #pragma unroll
@@ -222,7 +223,7 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
                 const int tx_i = (int)(tile % p.tiles_x);
                 const int ty_i = (int)((tile / p.tiles_x) % p.tiles_y);
                 const long long nz = tile / tiles_per_plane;
-                const int z = (int)(nz % p.Z), n = (int)(nz / p.Z);
+                const int z = p.z0 + (int)(nz % p.ZW), n = (int)(nz / p.ZW);
                 const int x0 = tx_i * TX, y0 = ty_i * TR;
                 // The next tile's halo rows go out once this tile's first `S` channels are
                 // requested: by then the ring is what the producer waits on anyway.
@@ -258,7 +259,7 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
         const int tx_i = (int)(tile % p.tiles_x);
         const int ty_i = (int)((tile / p.tiles_x) % p.tiles_y);
         const long long nz = tile / tiles_per_plane;
-        const int z = (int)(nz % p.Z), n = (int)(nz / p.Z);
+        const int z = p.z0 + (int)(nz % p.ZW), n = (int)(nz / p.ZW);
         const int x0 = tx_i * TX, y0 = ty_i * TR;
 
         // ---- turn the halo rows (landed by TMA) into the folded rows of m, in place ----

@@ -187,9 +187,10 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
     p.d = a.d, p.Dp = (a.d + 3) & ~3;
     const int TX = pl.txq16 ? 64 : 128;
     const int TR = (kConsumers / (TX / 4)) * pl.j;
+    get_z_window((int)g.z, &p.z0, &p.ZW);
     p.tiles_x = (int)ceil_div(g.x, TX);
     p.tiles_y = (int)ceil_div(g.y, TR);
-    p.num_tiles = (long long)p.tiles_x * p.tiles_y * g.z * g.n;
+    p.num_tiles = (long long)p.tiles_x * p.tiles_y * p.ZW * g.n;
     p.stages = pl.stages;
     p.status = tma::device_status_ptr(device);
     if (!p.status) MSD_FAIL(MSD_ERR_CUDA, "fused backward: cannot locate the device status word");

@@ -191,9 +191,18 @@ int forward_nd(bool relu, const View &in, const float *k, const float *bias, con
     }
     p.k = k, p.bias = bias;
     p.N = (int)in.n, p.C = (int)in.c, p.Z = (int)in.z, p.Y = (int)in.y, p.X = (int)in.x;
+    get_z_window((int)in.z, &p.z0, &p.ZW);
+    const int gather_z0 = p.z0, gather_zw = p.ZW;
+    if (nd == 3) {
+        // the z-gather of plane z reads the partial sums of planes z - d and z + d: compute
+        // those for the window widened by d on both sides (clipped to the local buffer)
+        const int lo = p.z0 - d < 0 ? 0 : p.z0 - d;
+        const int hi = p.z0 + p.ZW + d > (int)in.z ? (int)in.z : p.z0 + p.ZW + d;
+        p.z0 = lo, p.ZW = hi - lo;
+    }
     p.tiles_x = (int)ceil_div(in.x, kFwdTW);
     p.tiles_y = (int)ceil_div(in.y, var->th);
-    p.num_tiles = (long long)p.tiles_x * p.tiles_y * in.z * in.n;
+    p.num_tiles = (long long)p.tiles_x * p.tiles_y * p.ZW * in.n;
     p.stages = stages;
     p.relu = relu ? 1 : 0;
     p.status = tma::device_status_ptr(device);
@@ -204,12 +213,12 @@ int forward_nd(bool relu, const View &in, const float *k, const float *bias, con
     if (rc) return rc;
     count_launch(true);
     if (nd == 3) {
-        const int64_t quads = vox / 4;
+        const int64_t quads = in.n * (int64_t)gather_zw * in.y * in.x / 4;
         int64_t g = ceil_div(quads, 256);
         const int64_t gmax = (int64_t)sm_count(device) * 16;
         if (g > gmax) g = gmax;
         zgather_kernel<<<(unsigned)g, 256, 0, s>>>((const float *)ws, (float *)out.p, out.sn, out.sz, out.sy, bias, (int)in.n, (int)in.z, (int)in.y,
-                                                   (int)in.x, d, relu ? 1 : 0);
+                                                   (int)in.x, gather_z0, gather_zw, d, relu ? 1 : 0);
         count_launch(true);
         MSD_CUDA_TRY(cudaGetLastError());
     }

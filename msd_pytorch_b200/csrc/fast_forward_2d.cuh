@@ -46,6 +46,7 @@ struct Fwd2dParams {
     const float *k;     // [C][NT*9]
     const float *bias;  // [1]
     int N, C, Z, Y, X;
+    int z0, ZW;  // planes [z0, z0 + ZW) are computed (the whole volume unless a z-slab window is set)
     int tiles_x, tiles_y;
     long long num_tiles;
     int stages;
@@ -147,7 +148,7 @@ forward2d_kernel(const __grid_constant__ CUtensorMap map, const Fwd2dParams p) {
                 const int tx_i = (int)(tile % p.tiles_x);
                 const int ty_i = (int)((tile / p.tiles_x) % p.tiles_y);
                 const long long nz = tile / tiles_per_image;
-                const int z = (int)(nz % p.Z), n = (int)(nz / p.Z);
+                const int z = p.z0 + (int)(nz % p.ZW), n = (int)(nz / p.ZW);
                 const int bx = tx_i * TW - DP, by = ty_i * TH - D;
                 for (int c = 0; c < p.C; ++c, ++it) {
                     const int s = it % S;
@@ -173,7 +174,7 @@ forward2d_kernel(const __grid_constant__ CUtensorMap map, const Fwd2dParams p) {
         const int tx_i = (int)(tile % p.tiles_x);
         const int ty_i = (int)((tile / p.tiles_x) % p.tiles_y);
         const long long nz = tile / tiles_per_image;
-        const int z = (int)(nz % p.Z), n = (int)(nz / p.Z);
+        const int z = p.z0 + (int)(nz % p.ZW), n = (int)(nz / p.ZW);
         const int x0 = tx_i * TW, y0 = ty_i * TH;
 
         // Shared-memory offset of each lattice row (reflected at the top/bottom border and
@@ -244,9 +245,9 @@ forward2d_kernel(const __grid_constant__ CUtensorMap map, const Fwd2dParams p) {
 // u dense [3][N][Z][Y][X], four voxels per thread.
 __global__ void __launch_bounds__(256)
 zgather_kernel(const float *__restrict__ u, float *__restrict__ out, int64_t out_sn, int64_t out_sz, int64_t out_sy, const float *__restrict__ bias,
-               int N, int Z, int Y, int X, int d, int relu) {
+               int N, int Z, int Y, int X, int z0, int ZW, int d, int relu) {
     const int xq = X / 4;
-    const int64_t total = (int64_t)N * Z * Y * xq;
+    const int64_t total = (int64_t)N * ZW * Y * xq;
     const int64_t plane = (int64_t)Y * X, vol = plane * Z, ust = vol * N;
     const float b = bias[0];
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -254,7 +255,7 @@ zgather_kernel(const float *__restrict__ u, float *__restrict__ out, int64_t out
         int64_t r = i / xq;
         const int y = (int)(r % Y);
         r /= Y;
-        const int z = (int)(r % Z), n = (int)(r / Z);
+        const int z = z0 + (int)(r % ZW), n = (int)(r / ZW);
         const int zm = reflect(z - d, Z), zp = reflect(z + d, Z);
         const int64_t off = (int64_t)n * vol + (int64_t)y * X + 4 * x4;
         const float4 a0 = *reinterpret_cast<const float4 *>(u + off + zm * plane);

@@ -33,5 +33,19 @@ int tuning_get(int family, int dilation) {
     return g_choice[family][dilation];
 }
 
+static thread_local int t_z0 = 0, t_z1 = 0;
+
+void set_z_window(int z0, int z1) { t_z0 = z0, t_z1 = z1; }
+
+void get_z_window(int Z, int *z0, int *zw) {
+    if (t_z1 > t_z0 && t_z0 >= 0 && t_z1 <= Z) {
+        *z0 = t_z0;
+        *zw = t_z1 - t_z0;
+    } else {
+        *z0 = 0;
+        *zw = Z;
+    }
+}
+
 }  // namespace fast
 }  // namespace msd

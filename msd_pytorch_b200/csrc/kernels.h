@@ -19,6 +19,12 @@ int backward_bias(int dtype, bool relu, const View *out, const View &gout, void 
 namespace fast {
 
 enum Family { FWD2D = 0, BWD2D = 1, FWD3D = 2, BWD3D = 3, NUM_FAMILIES = 4 };
+
+// z-slab window of the calling thread: while set (z1 > z0), the tuned 3D kernels compute
+// only the planes [z0, z1) of the tensors they are given and read the planes around them as
+// halo.  Used by the slab entry points of the C ABI; cleared again before they return.
+void set_z_window(int z0, int z1);
+void get_z_window(int Z, int *z0, int *zw);
 int num_variants(int family);
 int tuning_set(int family, int dilation, int variant);
 int tuning_get(int family, int dilation);
