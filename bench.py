@@ -53,6 +53,14 @@ def algorithmic_bytes(depth, voxels):
     return 4 * voxels * (s1 + depth), 4 * voxels * (3 * s1 + 2 * depth)
 
 
+# DRAM traffic per launch measured by ncu (dram__bytes_read.sum + dram__bytes_write.sum) divided
+# by the algorithmic bytes of the captured launch; see profiles/fused_backward_2d_c2_layer50.md,
+# profiles/forward2d_c2_layer50.md and profiles/kernels_3d_c4_layer25.md.  The captures were
+# taken on one mid-depth layer of the same shapes; traffic grows with the channel count like the
+# algorithmic bytes do, so the ratio is applied to the average launch.
+NCU_TRAFFIC_RATIO = {("bwd", 2): 1234.1 / 1275.1, ("fwd", 2): 433.0 / 427.8, ("bwd", 3): 1254.8 / 1291.8, ("fwd", 3): 509.7 / 436.2}
+
+
 def measured_peak():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -167,6 +175,12 @@ def run_ours(args, cfg, rank, world, device):
     if args.strong:
         assert batch % world == 0
         batch //= world
+    tuned = None
+    if not args.no_autotune:
+        # per-shape launch autotuning (untimed set-up; winners are cached on disk)
+        from msd_pytorch_b200 import autotune
+
+        tuned = autotune.tune(batch, cfg["spatial"], max(2, cfg["depth"] // 2), range(1, 11), device=device, reps=3)
     model = build_model(cfg, device)
     params = grads_bucket(model)
     x, y = make_data(cfg, batch, 1000 + rank)
@@ -298,6 +312,7 @@ def run_ours(args, cfg, rank, world, device):
                                 "+Adam" if cfg["adam"] else "", 4 * voxels_rank * (1 + depth) / 1e9),
                 "parallelism": "dp%d" % world if world > 1 else "single",
                 "l2_policy": "inputs larger than L2",
+                "launch_variants": {k: [v[d] for d in sorted(v)] for k, v in tuned.items()} if tuned else "library defaults",
             },
             "e2e": {"value": total_vox / (ms_e2e * 1e-3), "unit": "voxels/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": int(xp.numel() * xp.element_size() + yp.numel() * yp.element_size()), "d2h_bytes_per_step": 4},
@@ -310,12 +325,14 @@ def run_ours(args, cfg, rank, world, device):
                 "bound": "hbm", "achieved": gbs_bwd, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": gbs_bwd / peak,
                 "frac_of_nominal_8TBs": gbs_bwd / 8000.0,
                 "algorithmic_bytes_per_launch": a_bwd / depth, "avg_launch_ms": ms_bwd / depth, "launches": depth,
-                "traffic": None,
+                "traffic": NCU_TRAFFIC_RATIO[("bwd", nd)] * a_bwd / depth,
+                "traffic_source": "ncu capture of one mid-depth layer, scaled by algorithmic bytes (profiles/)",
             },
             "roofline_forward": {
-                "kernel": "forward2d_kernel" if nd == 2 else "generic forward_kernel<3>",
+                "kernel": "forward2d_kernel" if nd == 2 else "forward2d_kernel<NT=3> + zgather_kernel",
                 "bound": "hbm", "achieved": gbs_fwd, "peak": peak, "unit": "GB/s", "frac": gbs_fwd / peak,
                 "algorithmic_bytes_per_launch": a_fwd / depth, "avg_launch_ms": ms_fwd / depth, "launches": depth,
+                "traffic": NCU_TRAFFIC_RATIO[("fwd", nd)] * a_fwd / depth,
             },
             "block_only": {"fwd_ms": ms_fwd, "bwd_ms": ms_bwd, "voxels_per_s": total_vox / ((ms_fwd + ms_bwd) * 1e-3),
                            "roofline_frac": (a_fwd + a_bwd) / ((ms_fwd + ms_bwd) * 1e-3) / 1e9 / peak},
@@ -418,6 +435,7 @@ def main():
     ap.add_argument("--strong", action="store_true", help="split the config's global batch over the ranks instead of fixing the per-rank batch")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ref-cuda", action="store_true")
+    ap.add_argument("--no-autotune", action="store_true", help="use the library's default launch variants")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     cfg = CONFIGS[args.config]

@@ -33,6 +33,7 @@
 // shared memory; at the end of the block the eight warp slots are added in warp order and
 // written to `part_k[block]`; a second kernel adds the blocks' partials in block order.
 #pragma once
+#include <type_traits>
 #include "common.cuh"
 #include "kernels.h"
 #include "tma.cuh"
@@ -118,6 +119,35 @@ __device__ __forceinline__ float warp_reduce_scatter(float (&v)[NV], int lane) {
     if (NV == 16) r += __shfl_xor_sync(0xffffffffu, r, 16);
     return r;
 }
+
+// The same for CU independent vectors at once (their shuffle chains interleave).
+template <int NV, int CU>
+__device__ __forceinline__ void warp_reduce_scatter_multi(float (&v)[CU][NV], int lane, float (&out)[CU]) {
+#pragma unroll
+    for (int h = NV / 2; h >= 1; h >>= 1) {
+        const bool up = (lane & h) != 0;
+#pragma unroll
+        for (int i = 0; i < h; ++i)
+#pragma unroll
+            for (int u = 0; u < CU; ++u) {
+                const float send = up ? v[u][i] : v[u][i + h];
+                const float keep = up ? v[u][i + h] : v[u][i];
+                v[u][i] = keep + __shfl_xor_sync(0xffffffffu, send, h);
+            }
+    }
+#pragma unroll
+    for (int u = 0; u < CU; ++u) {
+        float r = v[u][0];
+        if (NV == 16) r += __shfl_xor_sync(0xffffffffu, r, 16);
+        out[u] = r;
+    }
+}
+
+// Channels processed per loop iteration.
+template <int ND, int J>
+struct BwdUnroll {
+    static constexpr int kChannels = (ND == 2) ? 2 : 1;
+};
 
 __device__ __forceinline__ float4 ld4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
 
@@ -360,61 +390,86 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
         float *gi_tile = DO_X ? p.gin + n * p.gi_sn + z * p.gi_sz + (int64_t)y0 * p.gi_sy + x0 + 4 * xq : nullptr;
 
         // ---- stream the C input channels past the registers ----
+        // CU channels are processed per iteration so that their FMA blocks and shuffle
+        // reduce-scatters (long dependent chains) interleave.
         MSD_T(t4);
-        for (int c = 0; c < p.C; ++c, ++it) {
-            const int s = it % S;
-            tma::wait_parity(&full[s], (it / S) & 1u, abort_flag, p.status, 2);
-            const float *stage = ring + s * STAGE;
-            float4 a[J], g[J];
+        auto body = [&](auto cu_tag, int c) {
+            constexpr int CU = decltype(cu_tag)::value;
+            float4 a[CU][J], g[CU][J];
 #pragma unroll
-            for (int j = 0; j < J; ++j) {
-                const int idx = (rpass + RPP * j) * TX + 4 * xq;
-                if (DO_K) a[j] = ld4(stage + idx);  // zero outside the image (TMA fill)
-                if (DO_X) g[j] = ld4(stage + (DO_K ? TR * TX : 0) + idx);
-            }
-            __syncwarp();
-            if (lane == 0) tma::mbar_arrive(&empty[s]);
-
-            if (DO_X) {
-                float w[TAPS_PAD];
-                const float4 *wp = reinterpret_cast<const float4 *>(wsm + c * TAPS_PAD);
-#pragma unroll
-                for (int i = 0; i < TAPS_PAD / 4; ++i) {
-                    const float4 t4 = wp[i];
-                    w[4 * i + 0] = t4.x, w[4 * i + 1] = t4.y, w[4 * i + 2] = t4.z, w[4 * i + 3] = t4.w;
-                }
-                const bool live = !*abort_flag;
+            for (int u = 0; u < CU; ++u) {
+                const int s = (it + u) % S;
+                tma::wait_parity(&full[s], ((it + u) / S) & 1u, abort_flag, p.status, 2);
+                const float *stage = ring + s * STAGE;
 #pragma unroll
                 for (int j = 0; j < J; ++j) {
-                    float gv[4] = {g[j].x, g[j].y, g[j].z, g[j].w};
+                    const int idx = (rpass + RPP * j) * TX + 4 * xq;
+                    if (DO_K) a[u][j] = ld4(stage + idx);  // zero outside the image (TMA fill)
+                    if (DO_X) g[u][j] = ld4(stage + (DO_K ? TR * TX : 0) + idx);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) {
 #pragma unroll
-                    for (int t = 0; t < TAPS; ++t)
+                for (int u = 0; u < CU; ++u) tma::mbar_arrive(&empty[(it + u) % S]);
+            }
+            it += CU;
+
+            if (DO_X) {
+                const bool live = !*abort_flag;
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) gv[e] = fmaf(w[t], M[t][j * 4 + e], gv[e]);
-                    if (valid[j] && live)
-                        *reinterpret_cast<float4 *>(gi_tile + c * p.gi_sc + (int64_t)(rpass + RPP * j) * p.gi_sy) =
-                            make_float4(gv[0], gv[1], gv[2], gv[3]);
+                for (int u = 0; u < CU; ++u) {
+                    float w[TAPS_PAD];
+                    const float4 *wp = reinterpret_cast<const float4 *>(wsm + (c + u) * TAPS_PAD);
+#pragma unroll
+                    for (int i = 0; i < TAPS_PAD / 4; ++i) {
+                        const float4 t4 = wp[i];
+                        w[4 * i + 0] = t4.x, w[4 * i + 1] = t4.y, w[4 * i + 2] = t4.z, w[4 * i + 3] = t4.w;
+                    }
+#pragma unroll
+                    for (int j = 0; j < J; ++j) {
+                        float gv[4] = {g[u][j].x, g[u][j].y, g[u][j].z, g[u][j].w};
+#pragma unroll
+                        for (int t = 0; t < TAPS; ++t)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) gv[e] = fmaf(w[t], M[t][j * 4 + e], gv[e]);
+                        if (valid[j] && live)
+                            *reinterpret_cast<float4 *>(gi_tile + (c + u) * p.gi_sc + (int64_t)(rpass + RPP * j) * p.gi_sy) =
+                                make_float4(gv[0], gv[1], gv[2], gv[3]);
+                    }
                 }
             }
             if (DO_K) {
-                float acc[NV];
+                float acc[CU][NV];
 #pragma unroll
-                for (int t = 0; t < NV; ++t) {
-                    float s_ = 0.f;
-                    if (t < TAPS) {
+                for (int u = 0; u < CU; ++u)
 #pragma unroll
-                        for (int j = 0; j < J; ++j) {
-                            s_ = fmaf(a[j].x, M[t][j * 4 + 0], s_);
-                            s_ = fmaf(a[j].y, M[t][j * 4 + 1], s_);
-                            s_ = fmaf(a[j].z, M[t][j * 4 + 2], s_);
-                            s_ = fmaf(a[j].w, M[t][j * 4 + 3], s_);
+                    for (int t = 0; t < NV; ++t) {
+                        float s_ = 0.f;
+                        if (t < TAPS) {
+#pragma unroll
+                            for (int j = 0; j < J; ++j) {
+                                s_ = fmaf(a[u][j].x, M[t][j * 4 + 0], s_);
+                                s_ = fmaf(a[u][j].y, M[t][j * 4 + 1], s_);
+                                s_ = fmaf(a[u][j].z, M[t][j * 4 + 2], s_);
+                                s_ = fmaf(a[u][j].w, M[t][j * 4 + 3], s_);
+                            }
                         }
+                        acc[u][t] = s_;
                     }
-                    acc[t] = s_;
+                float tot[CU];
+                warp_reduce_scatter_multi<NV, CU>(acc, lane, tot);
+                if (lane < TAPS) {
+#pragma unroll
+                    for (int u = 0; u < CU; ++u) wacc[(warp * p.C + c + u) * TAPS_PAD + lane] += tot[u];
                 }
-                const float tot = warp_reduce_scatter<NV>(acc, lane);
-                if (lane < TAPS) wacc[(warp * p.C + c) * TAPS_PAD + lane] += tot;
             }
+        };
+        {
+            constexpr int CUMAX = BwdUnroll<ND, J>::kChannels;
+            int c = 0;
+            for (; c + CUMAX <= p.C; c += CUMAX) body(std::integral_constant<int, CUMAX>{}, c);
+            for (; c < p.C; ++c) body(std::integral_constant<int, 1>{}, c);
         }
         MSD_T(t5);
         MSD_TADD(0, t0, t1);  // barrier at tile start

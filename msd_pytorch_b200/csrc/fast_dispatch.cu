@@ -8,9 +8,11 @@ bool forward_nd_supported(const View &in, const View &out, int nd, int d, const 
 int forward_nd(bool relu, const View &in, const float *k, const float *bias, const View &out, int nd, int d, void *ws, size_t wsb, int device,
                cudaStream_t s);
 
+int num_forward2d_variants();
+
 int num_variants(int family) {
     switch (family) {
-        case FWD2D: return 3;  // lattice rows x column segments per thread
+        case FWD2D: return num_forward2d_variants();  // lattice rows x column segments x tile width
         case BWD2D: return 2;  // 4 / 8 voxels per thread
         case FWD3D: return 2;  // 4 / 2 column segments per thread
         default: return 1;

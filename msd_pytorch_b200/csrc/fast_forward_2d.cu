@@ -84,10 +84,10 @@ int get_tensor_map(int device, const void *ptr, int rank, const int64_t *dims, c
 }
 
 // ---- kernel variants ----------------------------------------------------------------------
-template <int D, int R, int Q, int K, int NT>
+template <int D, int R, int Q, int K, int NT, int TW>
 static int launch_fwd2d(const CUtensorMap &map, const Fwd2dParams &p, int grid, int stages, cudaStream_t s) {
-    using Cfg = Fwd2dCfg<D, R, Q, K>;
-    auto kern = forward2d_kernel<D, R, Q, K, NT>;
+    using Cfg = Fwd2dCfg<D, R, Q, K, TW>;
+    auto kern = forward2d_kernel<D, R, Q, K, NT, TW>;
     const size_t smem = 256 + (size_t)stages * Cfg::STAGE_BYTES + (size_t)((p.C * (NT == 3 ? 28 : 12) + 31) & ~31) * 4;
     MSD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<grid, Cfg::THREADS, smem, s>>>(map, p);
@@ -95,37 +95,49 @@ static int launch_fwd2d(const CUtensorMap &map, const Fwd2dParams &p, int grid, 
     return MSD_OK;
 }
 
-#define V(D, R, Q, K, NT)                                                                                                   \
-    {                                                                                                                       \
-        launch_fwd2d<D, R, Q, K, NT>, Fwd2dCfg<D, R, Q, K>::THREADS, Fwd2dCfg<D, R, Q, K>::TH, Fwd2dCfg<D, R, Q, K>::BH,        \
-            Fwd2dCfg<D, R, Q, K>::BW, Fwd2dCfg<D, R, Q, K>::STAGE_BYTES                                                       \
+#define V(D, R, Q, K, NT, TW)                                                                                                   \
+    {                                                                                                                           \
+        launch_fwd2d<D, R, Q, K, NT, TW>, Fwd2dCfg<D, R, Q, K, TW>::THREADS, Fwd2dCfg<D, R, Q, K, TW>::TH, TW,                      \
+            Fwd2dCfg<D, R, Q, K, TW>::BH, Fwd2dCfg<D, R, Q, K, TW>::BW, Fwd2dCfg<D, R, Q, K, TW>::STAGE_BYTES                     \
     }
-// 2D, per dilation (index D-1): variant 0 = 4-row lattice, 4 column segments per thread;
-// variant 1 = 4-row lattice, 2 segments (twice the warps); variant 2 = 6-row lattice, 4 segments.
-static const Fwd2dVariant kFwd2d[10][3] = {
-    {V(1, 4, 8, 4, 1), V(1, 4, 8, 2, 1), V(1, 6, 8, 4, 1)},  {V(2, 4, 4, 4, 1), V(2, 4, 4, 2, 1), V(2, 6, 4, 4, 1)},
-    {V(3, 4, 3, 4, 1), V(3, 4, 3, 2, 1), V(3, 6, 3, 4, 1)},  {V(4, 4, 2, 4, 1), V(4, 4, 2, 2, 1), V(4, 6, 2, 4, 1)},
-    {V(5, 4, 2, 4, 1), V(5, 4, 2, 2, 1), V(5, 6, 2, 4, 1)},  {V(6, 4, 2, 4, 1), V(6, 4, 2, 2, 1), V(6, 6, 2, 4, 1)},
-    {V(7, 4, 2, 4, 1), V(7, 4, 2, 2, 1), V(7, 6, 1, 4, 1)},  {V(8, 4, 1, 4, 1), V(8, 4, 1, 2, 1), V(8, 6, 1, 4, 1)},
-    {V(9, 4, 1, 4, 1), V(9, 4, 1, 2, 1), V(9, 6, 1, 4, 1)},  {V(10, 4, 1, 4, 1), V(10, 4, 1, 2, 1), V(10, 6, 1, 4, 1)},
+// 2D, per dilation (index D-1).  Tile = (Q*R*D) rows x TW columns:
+//   variant 0: 4-row lattice, 4 column segments per thread, 128 columns
+//   variant 1: 4-row lattice, 2 segments (twice the warps), 128 columns
+//   variant 2: 6-row lattice, 4 segments, 128 columns
+//   variant 3: 4-row lattice, 2 segments, 64 columns (twice the tiles: finer load balance)
+//   variant 4: 3-row lattice, taller stacks (Q chosen for 36..48 rows), 4 segments, 128 columns
+static const int kNumFwd2dVariants = 5;
+static const Fwd2dVariant kFwd2d[10][kNumFwd2dVariants] = {
+    {V(1, 4, 8, 4, 1, 128), V(1, 4, 8, 2, 1, 128), V(1, 6, 8, 4, 1, 128), V(1, 4, 8, 2, 1, 64), V(1, 3, 14, 4, 1, 128)},
+    {V(2, 4, 4, 4, 1, 128), V(2, 4, 4, 2, 1, 128), V(2, 6, 4, 4, 1, 128), V(2, 4, 4, 2, 1, 64), V(2, 3, 7, 4, 1, 128)},
+    {V(3, 4, 3, 4, 1, 128), V(3, 4, 3, 2, 1, 128), V(3, 6, 3, 4, 1, 128), V(3, 4, 3, 2, 1, 64), V(3, 3, 5, 4, 1, 128)},
+    {V(4, 4, 2, 4, 1, 128), V(4, 4, 2, 2, 1, 128), V(4, 6, 2, 4, 1, 128), V(4, 4, 2, 2, 1, 64), V(4, 3, 4, 4, 1, 128)},
+    {V(5, 4, 2, 4, 1, 128), V(5, 4, 2, 2, 1, 128), V(5, 6, 2, 4, 1, 128), V(5, 4, 2, 2, 1, 64), V(5, 3, 3, 4, 1, 128)},
+    {V(6, 4, 2, 4, 1, 128), V(6, 4, 2, 2, 1, 128), V(6, 6, 2, 4, 1, 128), V(6, 4, 2, 2, 1, 64), V(6, 3, 2, 4, 1, 128)},
+    {V(7, 4, 2, 4, 1, 128), V(7, 4, 2, 2, 1, 128), V(7, 6, 1, 4, 1, 128), V(7, 4, 2, 2, 1, 64), V(7, 3, 2, 4, 1, 128)},
+    {V(8, 4, 1, 4, 1, 128), V(8, 4, 1, 2, 1, 128), V(8, 6, 1, 4, 1, 128), V(8, 4, 1, 2, 1, 64), V(8, 3, 2, 4, 1, 128)},
+    {V(9, 4, 1, 4, 1, 128), V(9, 4, 1, 2, 1, 128), V(9, 6, 1, 4, 1, 128), V(9, 4, 1, 2, 1, 64), V(9, 3, 1, 4, 1, 128)},
+    {V(10, 4, 1, 4, 1, 128), V(10, 4, 1, 2, 1, 128), V(10, 6, 1, 4, 1, 128), V(10, 4, 1, 2, 1, 64), V(10, 3, 1, 4, 1, 128)},
 };
 // 3D (three z-taps per staged plane), per dilation: variant 0 = 4-row lattice, 4 column
 // segments per thread; variant 1 = 4-row lattice, 2 segments (twice the warps, shorter tiles
 // where the block would otherwise exceed ~500 threads and run out of registers).
 static const Fwd2dVariant kFwd3d[10][2] = {
-    {V(1, 4, 8, 4, 3), V(1, 4, 6, 2, 3)}, {V(2, 4, 4, 4, 3), V(2, 4, 3, 2, 3)}, {V(3, 4, 3, 4, 3), V(3, 4, 2, 2, 3)},
-    {V(4, 4, 2, 4, 3), V(4, 4, 1, 2, 3)}, {V(5, 4, 2, 4, 3), V(5, 4, 1, 2, 3)}, {V(6, 4, 2, 4, 3), V(6, 4, 1, 2, 3)},
-    {V(7, 4, 2, 4, 3), V(7, 4, 1, 2, 3)}, {V(8, 4, 1, 4, 3), V(8, 4, 1, 2, 3)}, {V(9, 4, 1, 4, 3), V(9, 4, 1, 2, 3)},
-    {V(10, 4, 1, 4, 3), V(10, 4, 1, 2, 3)},
+    {V(1, 4, 8, 4, 3, 128), V(1, 4, 6, 2, 3, 128)}, {V(2, 4, 4, 4, 3, 128), V(2, 4, 3, 2, 3, 128)}, {V(3, 4, 3, 4, 3, 128), V(3, 4, 2, 2, 3, 128)},
+    {V(4, 4, 2, 4, 3, 128), V(4, 4, 1, 2, 3, 128)}, {V(5, 4, 2, 4, 3, 128), V(5, 4, 1, 2, 3, 128)}, {V(6, 4, 2, 4, 3, 128), V(6, 4, 1, 2, 3, 128)},
+    {V(7, 4, 2, 4, 3, 128), V(7, 4, 1, 2, 3, 128)}, {V(8, 4, 1, 4, 3, 128), V(8, 4, 1, 2, 3, 128)}, {V(9, 4, 1, 4, 3, 128), V(9, 4, 1, 2, 3, 128)},
+    {V(10, 4, 1, 4, 3, 128), V(10, 4, 1, 2, 3, 128)},
 };
 #undef V
 
 static const size_t kFwdSmemBudget = 220 * 1024;
 
+int num_forward2d_variants() { return kNumFwd2dVariants; }
+
 static bool fwd_plan(const View &in, int nd, int d, const Fwd2dVariant **var, int *stages) {
     if (d < 1 || d > 10) return false;
     const int wp = nd == 3 ? 28 : 12;
-    const int nvar = nd == 3 ? 2 : 3;
+    const int nvar = nd == 3 ? 2 : kNumFwd2dVariants;
     int v = tuning_get(nd == 3 ? FWD3D : FWD2D, d);
     if (v < 0 || v >= nvar) v = 0;
     const Fwd2dVariant *cand = nd == 3 ? &kFwd3d[d - 1][v] : &kFwd2d[d - 1][v];
@@ -200,7 +212,7 @@ int forward_nd(bool relu, const View &in, const float *k, const float *bias, con
         const int hi = p.z0 + p.ZW + d > (int)in.z ? (int)in.z : p.z0 + p.ZW + d;
         p.z0 = lo, p.ZW = hi - lo;
     }
-    p.tiles_x = (int)ceil_div(in.x, kFwdTW);
+    p.tiles_x = (int)ceil_div(in.x, var->tw);
     p.tiles_y = (int)ceil_div(in.y, var->th);
     p.num_tiles = (long long)p.tiles_x * p.tiles_y * p.ZW * in.n;
     p.stages = stages;

@@ -9,7 +9,7 @@
 // shared-memory ring; the producer runs up to `stages` channels ahead, across tile
 // boundaries.  Blocks are persistent and take tiles in a fixed round-robin order.
 //
-// Compute: the tile has Q*R*D rows and 128 columns.  A warp owns the rows
+// Compute: the tile has Q*R*D rows and TW (128 or 64) columns.  A warp owns the rows
 // {base + i + j*D, j < R} of one residue class i modulo D ("row lattice") and its 32 lanes
 // own K column segments 32 apart.  Output rows j and j+1 of a lattice share two of their
 // three input rows, so per channel a thread loads (R+2)*3*K values from shared memory for
@@ -37,7 +37,6 @@
 namespace msd {
 namespace fast {
 
-constexpr int kFwdTW = 128;  // tile width
 constexpr int kFwdMaxStages = 8;
 
 struct Fwd2dParams {
@@ -54,14 +53,14 @@ struct Fwd2dParams {
     int *status;
 };
 
-template <int D, int R, int Q, int K>
+template <int D, int R, int Q, int K, int TW>
 struct Fwd2dCfg {
-    static constexpr int XW = kFwdTW / (32 * K);    // warps side by side along x
+    static constexpr int XW = TW / (32 * K);        // warps side by side along x
     static constexpr int NCW = Q * D * XW;          // compute warps
     static constexpr int THREADS = NCW * 32 + 32;   // + producer warp
     static constexpr int TH = Q * R * D;            // tile rows
     static constexpr int DP = (D + 3) & ~3;
-    static constexpr int BW = kFwdTW + 2 * DP;      // box columns
+    static constexpr int BW = TW + 2 * DP;          // box columns
     static constexpr int BH = TH + 2 * D;           // box rows
     static constexpr int STAGE_BYTES = ((BH * BW * 4) + 127) & ~127;
     static constexpr int STAGE = STAGE_BYTES / 4;
@@ -105,13 +104,12 @@ __device__ __forceinline__ void fwd2d_channel(float (&acc)[NT][R][K], const floa
     }
 }
 
-template <int D, int R, int Q, int K, int NT>
-__global__ void __launch_bounds__(Fwd2dCfg<D, R, Q, K>::THREADS, 1)
+template <int D, int R, int Q, int K, int NT, int TW>
+__global__ void __launch_bounds__(Fwd2dCfg<D, R, Q, K, TW>::THREADS, 1)
 forward2d_kernel(const __grid_constant__ CUtensorMap map, const Fwd2dParams p) {
     constexpr int WP = (NT == 3) ? 28 : 12;  // weights per channel, padded to whole float4s
-    using Cfg = Fwd2dCfg<D, R, Q, K>;
+    using Cfg = Fwd2dCfg<D, R, Q, K, TW>;
     constexpr int NCW = Cfg::NCW, XW = Cfg::XW, TH = Cfg::TH, DP = Cfg::DP, BW = Cfg::BW, BH = Cfg::BH, STAGE = Cfg::STAGE;
-    constexpr int TW = kFwdTW;
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw);
@@ -279,7 +277,7 @@ zgather_kernel(const float *__restrict__ u, float *__restrict__ out, int64_t out
 typedef int (*Fwd2dLaunchFn)(const CUtensorMap &, const Fwd2dParams &, int grid, int stages, cudaStream_t);
 struct Fwd2dVariant {
     Fwd2dLaunchFn launch;
-    int threads, th, bh, bw, stage_bytes;
+    int threads, th, tw, bh, bw, stage_bytes;
 };
 
 }  // namespace fast
