@@ -82,7 +82,7 @@ static int backward_x_impl(const char *op, bool relu, int dtype, const msd_tenso
     MSD_CUDA_TRY(g.status);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == MSD_F32 && gout.c == 1) {
-        fast::BackwardArgs a{relu ? &out : nullptr, &gout, nullptr, &gin, (const float *)kernel, nullptr, nullptr, nd, d, nullptr, 0, nullptr};
+        fast::BackwardArgs a{relu ? &out : nullptr, &gout, nullptr, &gin, (const float *)kernel, nullptr, nullptr, nd, d, nullptr, 0, nullptr, -1};
         if (fast::backward_supported(a)) return fast::backward(a, device, s);
     }
     return generic::backward_x(dtype, relu, relu ? &out : nullptr, gout, kernel, gin, nd, d, s);
@@ -107,7 +107,7 @@ static int backward_k_impl(const char *op, bool relu, int dtype, const msd_tenso
     MSD_CUDA_TRY(g.status);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == MSD_F32 && gout.c == 1) {
-        fast::BackwardArgs a{relu ? &out : nullptr, &gout, &in, nullptr, nullptr, (float *)grad_kernel, nullptr, nd, d, ws, wsb, nullptr};
+        fast::BackwardArgs a{relu ? &out : nullptr, &gout, &in, nullptr, nullptr, (float *)grad_kernel, nullptr, nd, d, ws, wsb, nullptr, -1};
         if (fast::backward_supported(a)) return fast::backward(a, device, s);
     }
     return generic::backward_k(dtype, relu, relu ? &out : nullptr, gout, in, grad_kernel, nd, d, ws, wsb, s);
@@ -274,6 +274,10 @@ int msd_block_backward(int dtype, const msd_tensor_t *result, const msd_tensor_t
     const size_t es = dtype == MSD_F64 ? 8 : 4;
     fast::ReduceList pending;
     pending.count = 0, pending.ws_used = 0;
+    // `gated`: the gradient channel the next layer reads is already multiplied by that layer's
+    // ReLU gate (done by the kernel of the layer above when it stores that channel), so the
+    // layer's kernel needs no halo of the activation.  The topmost channel is gated up front.
+    bool gated = false;
     for (int i = depth - 1; i >= 0; --i) {
         const int64_t n_i = c_in + (int64_t)i * width;
         View out = channel_slice(r, n_i, width, es);
@@ -284,14 +288,24 @@ int msd_block_backward(int dtype, const msd_tensor_t *result, const msd_tensor_t
         void *gk = grad_weights ? grad_weights[i] : nullptr;
         void *gb = grad_bias ? (char *)grad_bias + (size_t)i * width * es : nullptr;
         if (dtype == MSD_F32 && width == 1) {
-            fast::BackwardArgs a{&out, &gout, &in, &gin, (const float *)weights[i], (float *)gk, (float *)gb, nd, d, workspace, workspace_bytes, &pending};
+            // gate the channel below on store when that layer will run the fused kernel too
+            const bool can_gate_next = gk != nullptr && i > 0 && n_i - 1 >= c_in;
+            fast::BackwardArgs a{&out, &gout, &in, &gin, (const float *)weights[i], (float *)gk, (float *)gb, nd, d, workspace, workspace_bytes,
+                                 &pending, can_gate_next ? (int)(n_i - 1) : -1};
             if (fast::backward_supported(a)) {
+                if (!gated && i == depth - 1 && fast::gate_channel_supported(gout, out)) {
+                    if ((rc = fast::gate_channel(gout, out, device, s))) return rc;
+                    gated = true;
+                }
+                if (gated) a.out = nullptr;
                 if ((rc = fast::backward(a, device, s))) return rc;
+                gated = can_gate_next;
                 continue;
             }
         }
         // the generic kernels use the workspace from its start: finish pending reductions first
         if ((rc = fast::flush_reductions(&pending, s))) return rc;
+        if (gated) MSD_FAIL(MSD_ERR_UNSUPPORTED, "msd_block_backward: layer %d cannot run the tuned kernel after the layer above gated its gradient", i);
         if ((rc = generic::backward_x(dtype, true, &out, gout, weights[i], gin, nd, d, s))) return rc;
         if (gk && (rc = generic::backward_k(dtype, true, &out, gout, in, gk, nd, d, workspace, workspace_bytes, s))) return rc;
         if (gb && (rc = generic::backward_bias(dtype, true, &out, gout, gb, workspace, workspace_bytes, s))) return rc;
@@ -339,7 +353,7 @@ int msd_slab_layer_backward(const msd_tensor_t *result, const msd_tensor_t *grad
     MSD_CUDA_TRY(g.status);
     View out = channel_slice(r, n_in, 1, 4), in = channel_slice(r, 0, n_in, 4);
     View gout = channel_slice(gr, n_in, 1, 4), gin = channel_slice(gr, 0, n_in, 4);
-    fast::BackwardArgs a{&out, &gout, &in, &gin, (const float *)weight, (float *)grad_weight, (float *)grad_bias, 3, dilation, workspace, workspace_bytes, nullptr};
+    fast::BackwardArgs a{&out, &gout, &in, &gin, (const float *)weight, (float *)grad_weight, (float *)grad_bias, 3, dilation, workspace, workspace_bytes, nullptr, -1};
     if (!fast::backward_supported(a))
         MSD_FAIL(MSD_ERR_UNSUPPORTED, "msd_slab_layer_backward: shape, alignment, dilation or workspace not supported by the tuned 3D kernel");
     fast::set_z_window(z_begin, z_end);

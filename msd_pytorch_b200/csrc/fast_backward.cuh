@@ -51,9 +51,11 @@
 namespace msd {
 namespace fast {
 
-constexpr int kConsumerWarps = 8;
-constexpr int kConsumers = kConsumerWarps * 32;
-constexpr int kBwdThreads = kConsumers + 32;  // + one producer warp
+// Consumer warps per block (+ one producer warp).  Registers are allocated per four warps:
+// 8 + 1 and 11 + 1 warps both leave 168 registers per thread, so the register-hungry 3D
+// kernel runs 11 consumer warps; 2D keeps 8 (its 16-row tiles divide the benchmark images).
+constexpr int bwd_consumer_warps(int nd) { return nd == 3 ? 11 : 8; }
+constexpr int kMaxConsumerWarps = 11;
 constexpr int kMaxStages = 8;
 
 struct BwdParams {
@@ -74,6 +76,7 @@ struct BwdParams {
     int tiles_x, tiles_y;
     long long num_tiles;
     int stages;
+    int mask_channel;  // input channel whose new gradient is stored already gated by in[c] > 0 (-1: none)
     int *status;
     unsigned long long *timing;  // developer instrumentation, null in normal builds
 };
@@ -159,11 +162,12 @@ struct BwdOccupancy {
 };
 
 template <int ND, int TXQ, int J, bool DO_X, bool DO_K>
-__global__ void __launch_bounds__(kBwdThreads, BwdOccupancy<ND, J>::kBlocksPerSM)
+__global__ void __launch_bounds__(bwd_consumer_warps(ND) * 32 + 32, BwdOccupancy<ND, J>::kBlocksPerSM)
 fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_gin,
                       const __grid_constant__ CUtensorMap map_gout, const __grid_constant__ CUtensorMap map_out, const BwdParams p) {
     using T = BwdTraits<ND>;
     constexpr int RT = T::RT, TAPS = T::TAPS, TAPS_PAD = T::TAPS_PAD, NV = T::NV;
+    constexpr int kConsumerWarps = bwd_consumer_warps(ND), kConsumers = kConsumerWarps * 32, kBwdThreads = kConsumers + 32;
     constexpr int TX = TXQ * 4;
     constexpr int RPP = kConsumers / TXQ;  // rows per pass
     constexpr int TR = RPP * J;            // rows per tile
@@ -183,7 +187,9 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
     // TMA destinations first (128-byte aligned): halo rows of gout (turned into the folded
     // rows of m in place), halo rows of out, then the ring.
     float *rows = reinterpret_cast<float *>(smem_raw + 256);
-    const int halo_floats = ((RT * TR * TXP + 31) & ~31);
+    // each of the RT halo boxes gets a slot rounded up to 128 bytes (TMA destinations)
+    const int HSLOT = (TR * TXP + 31) & ~31;
+    const int halo_floats = RT * HSLOT;
     float *orows = rows + halo_floats;
     float *ring = orows + (gate ? halo_floats : 0);
     float *wsm = ring + (size_t)p.stages * STAGE;
@@ -237,7 +243,7 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
                 for (int rt = 0; rt < RT; ++rt) {
                     const int ty = (ND == 3) ? rt % 3 : rt, tz = (ND == 3) ? rt / 3 : 1;
                     const int by = y0 + p.d * (1 - ty), bz = z + p.d * (1 - tz);
-                    float *dg = rows + rt * TR * TXP, *dout = orows + rt * TR * TXP;
+                    float *dg = rows + rt * HSLOT, *dout = orows + rt * HSLOT;
                     if (ND == 3) {
                         tma::tensor_g2s_5d(dg, &map_gout, bx, by, bz, 0, n, halo_full);
                         if (gate) tma::tensor_g2s_5d(dout, &map_out, bx, by, bz, 0, n, halo_full);
@@ -304,9 +310,11 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
         const bool fold_rows = (y0 < p.d) || (y0 + TR + p.d > p.Y) || (ND == 3 && (z < p.d || z + p.d >= p.Z));
         for (int item = tid; item < RT * TR * quads; item += kConsumers) {
             const int rowid = item / quads, q4 = item - rowid * quads;
-            float4 g = *reinterpret_cast<const float4 *>(rows + rowid * TXP + 4 * q4);
+            const int rt_ = rowid / TR;
+            const int soff = rt_ * HSLOT + (rowid - rt_ * TR) * TXP + 4 * q4;  // slot of the row tap + row inside it
+            float4 g = *reinterpret_cast<const float4 *>(rows + soff);
             if (gate) {
-                const float4 o = *reinterpret_cast<const float4 *>(orows + rowid * TXP + 4 * q4);
+                const float4 o = *reinterpret_cast<const float4 *>(orows + soff);
                 g.x = o.x > 0.f ? g.x : 0.f;
                 g.y = o.y > 0.f ? g.y : 0.f;
                 g.z = o.z > 0.f ? g.z : 0.f;
@@ -339,7 +347,7 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
                         }
                 }
             }
-            *reinterpret_cast<float4 *>(rows + rowid * TXP + 4 * q4) = g;
+            *reinterpret_cast<float4 *>(rows + soff) = g;
         }
         MSD_T(t2);
         tma::named_barrier(1, kConsumers);
@@ -355,7 +363,7 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
             valid[j] = (y0 + r) < p.Y && (x0 + 4 * xq) < p.X;
 #pragma unroll
             for (int rt = 0; rt < RT; ++rt) {
-                const float *row = rows + (rt * TR + r) * TXP + p.Dp;  // row[i] <-> image x = x0 + i
+                const float *row = rows + rt * HSLOT + r * TXP + p.Dp;  // row[i] <-> image x = x0 + i
                 const float4 ctr = *reinterpret_cast<const float4 *>(row + 4 * xq);
                 const float cv[4] = {ctr.x, ctr.y, ctr.z, ctr.w};
 #pragma unroll
@@ -433,6 +441,14 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
                         for (int t = 0; t < TAPS; ++t)
 #pragma unroll
                             for (int e = 0; e < 4; ++e) gv[e] = fmaf(w[t], M[t][j * 4 + e], gv[e]);
+                        if (DO_K && (c + u) == p.mask_channel) {
+                            // this channel is the output of the layer below: hand its gradient
+                            // over already multiplied by that layer's ReLU gate
+                            gv[0] = a[u][j].x > 0.f ? gv[0] : 0.f;
+                            gv[1] = a[u][j].y > 0.f ? gv[1] : 0.f;
+                            gv[2] = a[u][j].z > 0.f ? gv[2] : 0.f;
+                            gv[3] = a[u][j].w > 0.f ? gv[3] : 0.f;
+                        }
                         if (valid[j] && live)
                             *reinterpret_cast<float4 *>(gi_tile + (c + u) * p.gi_sc + (int64_t)(rpass + RPP * j) * p.gi_sy) =
                                 make_float4(gv[0], gv[1], gv[2], gv[3]);

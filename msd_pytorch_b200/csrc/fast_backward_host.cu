@@ -24,7 +24,7 @@ extern "C" MSD_API void msd_debug_bwd_timing(unsigned long long *out) {
 #endif
 
 static const int kMaxFastDilation = 16;
-static const size_t kSmemBudget = 200 * 1024;
+static const size_t kSmemBudget = 220 * 1024;
 static const int kMaxGrid = 320;
 
 int sm_count(int device) {
@@ -66,9 +66,10 @@ static bool plan(const BackwardArgs &a, BwdPlan *pl) {
         j = tuned == 0 ? 1 : 2;  // variant 0: 4 voxels per thread, variant 1 (default): 8
     }
     for (; j >= 1; --j) {
-        const int TR = (kConsumers / (TX / 4)) * j;
-        const size_t halo = (size_t)(((int64_t)RT * TR * (TX + 2 * Dp) + 31) & ~31) * (a.out ? 2 : 1);
-        const size_t fixed = 256 + (size_t)4 * ((do_x ? C * TAPS_PAD : 0) + (do_k ? kConsumerWarps * C * TAPS_PAD : 0) + halo);
+        const int ncw = bwd_consumer_warps(nd);
+        const int TR = (ncw * 32 / (TX / 4)) * j;
+        const size_t halo = (size_t)RT * (((int64_t)TR * (TX + 2 * Dp) + 31) & ~31) * (a.out ? 2 : 1);
+        const size_t fixed = 256 + (size_t)4 * ((do_x ? C * TAPS_PAD : 0) + (do_k ? ncw * C * TAPS_PAD : 0) + halo);
         const size_t stage = (size_t)4 * ((do_x ? 1 : 0) + (do_k ? 1 : 0)) * TR * TX;
         // two resident blocks per SM for the small 2D variant when both fit
         int bps = (nd == 2 && j == 1) ? 2 : 1;
@@ -159,6 +160,48 @@ int flush_reductions(ReduceList *list, cudaStream_t s) {
     return MSD_OK;
 }
 
+// g = (a > 0) ? g : 0 on one channel (both views [N,1,Z,Y,X] with unit x-stride, X % 4 == 0):
+// gates the top gradient channel once before a block's backward, so that every layer's kernel
+// can read an already gated gradient.
+__global__ void __launch_bounds__(256)
+gate_channel_kernel(float *__restrict__ g, int64_t g_sn, int64_t g_sz, int64_t g_sy, const float *__restrict__ a, int64_t a_sn, int64_t a_sz,
+                    int64_t a_sy, int N, int Z, int Y, int X) {
+    const int xq = X / 4;
+    const int64_t total = (int64_t)N * Z * Y * xq;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int x4 = (int)(i % xq);
+        int64_t r = i / xq;
+        const int y = (int)(r % Y);
+        r /= Y;
+        const int z = (int)(r % Z), n = (int)(r / Z);
+        float4 *gp = reinterpret_cast<float4 *>(g + n * g_sn + z * g_sz + (int64_t)y * g_sy + 4 * x4);
+        const float4 av = *reinterpret_cast<const float4 *>(a + n * a_sn + z * a_sz + (int64_t)y * a_sy + 4 * x4);
+        float4 gv = *gp;
+        gv.x = av.x > 0.f ? gv.x : 0.f;
+        gv.y = av.y > 0.f ? gv.y : 0.f;
+        gv.z = av.z > 0.f ? gv.z : 0.f;
+        gv.w = av.w > 0.f ? gv.w : 0.f;
+        *gp = gv;
+    }
+}
+
+bool gate_channel_supported(const View &g, const View &a) {
+    return g.c == 1 && a.c == 1 && aligned_view(&g) && aligned_view(&a) && (g.x % 4) == 0 && g.n == a.n && g.z == a.z && g.y == a.y && g.x == a.x;
+}
+
+int gate_channel(const View &g, const View &a, int device, cudaStream_t s) {
+    const int64_t quads = g.n * g.z * g.y * (g.x / 4);
+    if (quads == 0) return MSD_OK;
+    int64_t grid = ceil_div(quads, 256);
+    const int64_t gmax = (int64_t)sm_count(device) * 16;
+    if (grid > gmax) grid = gmax;
+    gate_channel_kernel<<<(unsigned)grid, 256, 0, s>>>((float *)g.p, g.sn, g.sz, g.sy, (const float *)a.p, a.sn, a.sz, a.sy, (int)g.n, (int)g.z,
+                                                      (int)g.y, (int)g.x);
+    count_launch(true);
+    MSD_CUDA_TRY(cudaGetLastError());
+    return MSD_OK;
+}
+
 int backward(const BackwardArgs &a, int device, cudaStream_t s) {
     BwdPlan pl;
     if (!plan(a, &pl)) MSD_FAIL(MSD_ERR_UNSUPPORTED, "fused backward: shape not supported");
@@ -186,12 +229,13 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
     p.N = (int)g.n, p.C = (int)C, p.Z = (int)g.z, p.Y = (int)g.y, p.X = (int)g.x;
     p.d = a.d, p.Dp = (a.d + 3) & ~3;
     const int TX = pl.txq16 ? 64 : 128;
-    const int TR = (kConsumers / (TX / 4)) * pl.j;
+    const int TR = (bwd_consumer_warps(a.nd) * 32 / (TX / 4)) * pl.j;
     get_z_window((int)g.z, &p.z0, &p.ZW);
     p.tiles_x = (int)ceil_div(g.x, TX);
     p.tiles_y = (int)ceil_div(g.y, TR);
     p.num_tiles = (long long)p.tiles_x * p.tiles_y * p.ZW * g.n;
     p.stages = pl.stages;
+    p.mask_channel = (do_x && do_k) ? a.mask_channel : -1;
     p.status = tma::device_status_ptr(device);
     if (!p.status) MSD_FAIL(MSD_ERR_CUDA, "fused backward: cannot locate the device status word");
 #ifdef MSD_BWD_TIMING

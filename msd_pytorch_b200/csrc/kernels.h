@@ -70,7 +70,12 @@ struct BackwardArgs {
     void *ws;
     size_t wsb;
     ReduceList *defer;  // null: reduce right after the layer's kernel
+    int mask_channel;   // input channel whose updated gradient is stored gated by in[c] > 0; -1: none (needs gk)
 };
+// In-place gate of one gradient channel: g = (a > 0) ? g : 0 (views must satisfy the tuned
+// kernels' alignment rules).
+bool gate_channel_supported(const View &g, const View &a);
+int gate_channel(const View &g, const View &a, int device, cudaStream_t s);
 bool backward_supported(const BackwardArgs &a);
 size_t backward_workspace_bytes(int nd, int64_t c_in);
 int backward(const BackwardArgs &a, int device, cudaStream_t s);
