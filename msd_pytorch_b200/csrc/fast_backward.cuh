@@ -308,7 +308,8 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
         // Rows within d of a y (z) border also collect a mirrored source row; those few are
         // fetched with plain loads.
         const bool fold_rows = (y0 < p.d) || (y0 + TR + p.d > p.Y) || (ND == 3 && (z < p.d || z + p.d >= p.Z));
-        for (int item = tid; item < RT * TR * quads; item += kConsumers) {
+        // (with an already gated gradient and no border rows the boxes are final as they landed)
+        for (int item = tid; (gate || fold_rows) && item < RT * TR * quads; item += kConsumers) {
             const int rowid = item / quads, q4 = item - rowid * quads;
             const int rt_ = rowid / TR;
             const int soff = rt_ * HSLOT + (rowid - rt_ * TR) * TXP + 4 * q4;  // slot of the row tap + row inside it
@@ -423,6 +424,31 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
             }
             it += CU;
 
+            if (DO_K) {
+                float acc[CU][NV];
+#pragma unroll
+                for (int u = 0; u < CU; ++u)
+#pragma unroll
+                    for (int t = 0; t < NV; ++t) {
+                        float s_ = 0.f;
+                        if (t < TAPS) {
+#pragma unroll
+                            for (int j = 0; j < J; ++j) {
+                                s_ = fmaf(a[u][j].x, M[t][j * 4 + 0], s_);
+                                s_ = fmaf(a[u][j].y, M[t][j * 4 + 1], s_);
+                                s_ = fmaf(a[u][j].z, M[t][j * 4 + 2], s_);
+                                s_ = fmaf(a[u][j].w, M[t][j * 4 + 3], s_);
+                            }
+                        }
+                        acc[u][t] = s_;
+                    }
+                float tot[CU];
+                warp_reduce_scatter_multi<NV, CU>(acc, lane, tot);
+                if (lane < TAPS) {
+#pragma unroll
+                    for (int u = 0; u < CU; ++u) wacc[(warp * p.C + c + u) * TAPS_PAD + lane] += tot[u];
+                }
+            }
             if (DO_X) {
                 const bool live = !*abort_flag;
 #pragma unroll
@@ -453,31 +479,6 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
                             *reinterpret_cast<float4 *>(gi_tile + (c + u) * p.gi_sc + (int64_t)(rpass + RPP * j) * p.gi_sy) =
                                 make_float4(gv[0], gv[1], gv[2], gv[3]);
                     }
-                }
-            }
-            if (DO_K) {
-                float acc[CU][NV];
-#pragma unroll
-                for (int u = 0; u < CU; ++u)
-#pragma unroll
-                    for (int t = 0; t < NV; ++t) {
-                        float s_ = 0.f;
-                        if (t < TAPS) {
-#pragma unroll
-                            for (int j = 0; j < J; ++j) {
-                                s_ = fmaf(a[u][j].x, M[t][j * 4 + 0], s_);
-                                s_ = fmaf(a[u][j].y, M[t][j * 4 + 1], s_);
-                                s_ = fmaf(a[u][j].z, M[t][j * 4 + 2], s_);
-                                s_ = fmaf(a[u][j].w, M[t][j * 4 + 3], s_);
-                            }
-                        }
-                        acc[u][t] = s_;
-                    }
-                float tot[CU];
-                warp_reduce_scatter_multi<NV, CU>(acc, lane, tot);
-                if (lane < TAPS) {
-#pragma unroll
-                    for (int u = 0; u < CU; ++u) wacc[(warp * p.C + c + u) * TAPS_PAD + lane] += tot[u];
                 }
             }
         };
