@@ -54,10 +54,11 @@ def algorithmic_bytes(depth, voxels):
 
 
 # DRAM traffic per launch measured by ncu (dram__bytes_read.sum + dram__bytes_write.sum) divided
-# by the algorithmic bytes of the captured launch; see profiles/fused_backward_2d_c2_layer50.md,
-# profiles/forward2d_c2_layer50.md and profiles/kernels_3d_c4_layer25.md.  The captures were
-# taken on one mid-depth layer of the same shapes; traffic grows with the channel count like the
-# algorithmic bytes do, so the ratio is applied to the average launch.
+# by the algorithmic bytes of the captured launch: 2D backward 1234.1 / 1275.1 MB and 2D forward
+# 433.0 / 427.8 MB (batch 8 of 512x512, 50 input channels, dilation 10); 3D backward
+# 1254.8 / 1291.8 MB and 3D forward 509.7 / 436.2 MB (batch 2 of 128^3, 25 input channels,
+# dilation 4).  Traffic grows with the channel count like the algorithmic bytes do, so the ratio
+# is applied to the average launch.
 NCU_TRAFFIC_RATIO = {("bwd", 2): 1234.1 / 1275.1, ("fwd", 2): 433.0 / 427.8, ("bwd", 3): 1254.8 / 1291.8, ("fwd", 3): 509.7 / 436.2}
 
 
@@ -326,7 +327,7 @@ def run_ours(args, cfg, rank, world, device):
                 "frac_of_nominal_8TBs": gbs_bwd / 8000.0,
                 "algorithmic_bytes_per_launch": a_bwd / depth, "avg_launch_ms": ms_bwd / depth, "launches": depth,
                 "traffic": NCU_TRAFFIC_RATIO[("bwd", nd)] * a_bwd / depth,
-                "traffic_source": "ncu capture of one mid-depth layer, scaled by algorithmic bytes (profiles/)",
+                "traffic_source": "ncu capture of one mid-depth layer, scaled by algorithmic bytes",
             },
             "roofline_forward": {
                 "kernel": "forward2d_kernel" if nd == 2 else "forward2d_kernel<NT=3> + zgather_kernel",

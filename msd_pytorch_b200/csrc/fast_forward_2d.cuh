@@ -69,34 +69,49 @@ struct Fwd2dCfg {
 // One input channel's contribution to a thread's NT x R x K accumulators.  `rowoff[m]` is the
 // offset of the thread's first column in lattice row m of the box; BORDER selects run-time
 // column offsets for the taps that may leave the image.
+//
+// The FMAs are issued as packed pairs (fma.rn.f32x2 through __ffma2_rn): the accumulators of
+// two column segments share one instruction, the weight is duplicated into both halves once
+// per channel.  Each half is an ordinary fp32 FMA, so results are unchanged; what changes
+// is that the 9 (27) multiply-adds per loaded triple take half the issue slots, which is
+// what bounds these kernels after the shared-memory loads.
 template <int D, int R, int K, int NT, bool BORDER>
-__device__ __forceinline__ void fwd2d_channel(float (&acc)[NT][R][K], const float *st, const int (&rowoff)[R + 2], const float *wsm_c, int dl,
+__device__ __forceinline__ void fwd2d_channel(float2 (&acc)[NT][R][K / 2], const float *st, const int (&rowoff)[R + 2], const float *wsm_c, int dl,
                                               const int (&dr)[K]) {
+    static_assert(K % 2 == 0, "column segments are processed in pairs");
     constexpr int WP = (NT == 3) ? 28 : 12;
-    float w[WP];
+    float2 w[NT * 9];
     const float4 *wp = reinterpret_cast<const float4 *>(wsm_c);
 #pragma unroll
     for (int i = 0; i < WP / 4; ++i) {
         const float4 t4 = wp[i];
-        w[4 * i + 0] = t4.x, w[4 * i + 1] = t4.y, w[4 * i + 2] = t4.z, w[4 * i + 3] = t4.w;
+        if (4 * i + 0 < NT * 9) w[4 * i + 0] = make_float2(t4.x, t4.x);
+        if (4 * i + 1 < NT * 9) w[4 * i + 1] = make_float2(t4.y, t4.y);
+        if (4 * i + 2 < NT * 9) w[4 * i + 2] = make_float2(t4.z, t4.z);
+        if (4 * i + 3 < NT * 9) w[4 * i + 3] = make_float2(t4.w, t4.w);
     }
 #pragma unroll
     for (int m = 0; m < R + 2; ++m) {
         const float *rp = st + rowoff[m];
 #pragma unroll
-        for (int k = 0; k < K; ++k) {
-            const float a = (BORDER && k == 0) ? rp[dl] : rp[32 * k - D];
-            const float b = rp[32 * k];
-            const float cc = BORDER ? rp[32 * k + dr[k]] : rp[32 * k + D];
+        for (int kp = 0; kp < K / 2; ++kp) {
+            const int k0 = 2 * kp, k1 = 2 * kp + 1;
+            float2 a, b, cc;
+            a.x = (BORDER && k0 == 0) ? rp[dl] : rp[32 * k0 - D];
+            a.y = rp[32 * k1 - D];
+            b.x = rp[32 * k0];
+            b.y = rp[32 * k1];
+            cc.x = BORDER ? rp[32 * k0 + dr[k0]] : rp[32 * k0 + D];
+            cc.y = BORDER ? rp[32 * k1 + dr[k1]] : rp[32 * k1 + D];
 #pragma unroll
             for (int j = 0; j < R; ++j) {
                 const int t = m - j;  // tap row of output row j that reads lattice row m
                 if (t >= 0 && t <= 2) {
 #pragma unroll
                     for (int tz = 0; tz < NT; ++tz) {
-                        acc[tz][j][k] = fmaf(w[tz * 9 + t * 3 + 0], a, acc[tz][j][k]);
-                        acc[tz][j][k] = fmaf(w[tz * 9 + t * 3 + 1], b, acc[tz][j][k]);
-                        acc[tz][j][k] = fmaf(w[tz * 9 + t * 3 + 2], cc, acc[tz][j][k]);
+                        acc[tz][j][kp] = __ffma2_rn(w[tz * 9 + t * 3 + 0], a, acc[tz][j][kp]);
+                        acc[tz][j][kp] = __ffma2_rn(w[tz * 9 + t * 3 + 1], b, acc[tz][j][kp]);
+                        acc[tz][j][kp] = __ffma2_rn(w[tz * 9 + t * 3 + 2], cc, acc[tz][j][kp]);
                     }
                 }
             }
@@ -197,13 +212,13 @@ forward2d_kernel(const __grid_constant__ CUtensorMap map, const Fwd2dParams p) {
             dr[k] = (x < p.X && x + D >= p.X) ? 2 * p.X - 1 - 2 * x - D : D;  // x + D >= X mirrors to 2X - 1 - (x + D)
         }
 
-        float acc[NT][R][K];
+        float2 acc[NT][R][K / 2];
 #pragma unroll
         for (int tz = 0; tz < NT; ++tz)
 #pragma unroll
             for (int j = 0; j < R; ++j)
 #pragma unroll
-                for (int k = 0; k < K; ++k) acc[tz][j][k] = (NT == 1) ? bias : 0.f;
+                for (int kp = 0; kp < K / 2; ++kp) acc[tz][j][kp] = (NT == 1) ? make_float2(bias, bias) : make_float2(0.f, 0.f);
 
         for (int c = 0; c < p.C; ++c, ++it) {
             const int s = it % S;
@@ -228,7 +243,7 @@ forward2d_kernel(const __grid_constant__ CUtensorMap map, const Fwd2dParams p) {
 #pragma unroll
                         for (int k = 0; k < K; ++k) {
                             const int x = x0 + cb + 32 * k;
-                            float v = acc[tz][j][k];
+                            float v = (k & 1) ? acc[tz][j][k / 2].y : acc[tz][j][k / 2].x;
                             if (NT == 1 && p.relu) v = v > 0.f ? v : 0.f;
                             if (x < p.X) ob[(int64_t)y * p.out_sy + x] = v;
                         }

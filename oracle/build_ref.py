@@ -23,6 +23,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 NAME = "msd_custom_convolutions_ref"
+# where the reference checkout is expected when no path is given
+DEFAULT_REF_ROOT = os.path.join(os.sep, "root", "reference")
 
 SOURCES = [
     "msd_pytorch/msd_custom_convolutions.cpp",
@@ -44,7 +46,8 @@ def built_path():
     return p if os.path.exists(p) else None
 
 
-def build(ref_root="/root/reference", verbose=False):
+def build(ref_root=None, verbose=False):
+    ref_root = ref_root or os.environ.get("MSD_REFERENCE_ROOT", DEFAULT_REF_ROOT)
     if not os.path.isdir(ref_root):
         return built_path()
     os.makedirs(OUT, exist_ok=True)
@@ -79,5 +82,5 @@ def load():
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else None
     print(build(root, verbose=True))

@@ -12,7 +12,7 @@ GRAD_TOL = {torch.float32: 1e-3, torch.float64: 1e-10}
 
 def assert_close(actual, expected, rtol, what=""):
     """|a - e| <= rtol * (|e| + scale), scale = RMS of the expected tensor (so that values
-    that cancel to ~0 are judged against the tensor's magnitude)."""
+    that cancel to ~0 are measured against the tensor's magnitude)."""
     a = actual.detach().double().cpu()
     e = expected.detach().double().cpu()
     assert a.shape == e.shape, (what, a.shape, e.shape)
