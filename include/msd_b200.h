@@ -170,10 +170,18 @@ MSD_API int msd_slab_layer_forward(const msd_tensor_t *buffer, int n_in, const v
  * `gradients` on owned + halo planes (the caller has exchanged the gradient halo), adds the
  * input gradient into channels [0, n_in) of `gradients` on the owned planes, and this
  * slab's share of the weight / bias gradient into grad_weight / grad_bias (either may be
- * NULL); the caller sums those over the GPUs. */
+ * NULL); the caller sums those over the GPUs.
+ * `flags`: MSD_SLAB_GRADIENT_IS_GATED - channel n_in of `gradients` already holds the
+ * gradient multiplied by the ReLU gate (result > 0), so no halo of `result` is read;
+ * MSD_SLAB_GATE_CHANNEL_BELOW - store the updated gradient of channel n_in - 1 already
+ * multiplied by ITS gate (result[n_in - 1] > 0), ready for the next call (needs grad_weight).
+ * Chaining the two halves the halo traffic and shared memory of every layer but the top one. */
+#define MSD_SLAB_GRADIENT_IS_GATED 1
+#define MSD_SLAB_GATE_CHANNEL_BELOW 2
 MSD_API int msd_slab_layer_backward(const msd_tensor_t *result, const msd_tensor_t *gradients, int n_in,
                             const void *weight, int dilation, int z_begin, int z_end, void *grad_weight,
-                            void *grad_bias, void *workspace, size_t workspace_bytes, int device, void *stream);
+                            void *grad_bias, int flags, void *workspace, size_t workspace_bytes, int device,
+                            void *stream);
 
 /* ---- launch autotuner (replaces benchmarks/benchmark_block_sizes.py) ---- */
 

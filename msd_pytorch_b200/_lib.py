@@ -17,6 +17,7 @@ MSD_F32, MSD_F64 = 0, 1
 MAX_DIMS = 5
 
 FAMILY_FWD2D, FAMILY_BWD2D, FAMILY_FWD3D, FAMILY_BWD3D = 0, 1, 2, 3
+SLAB_GRADIENT_IS_GATED, SLAB_GATE_CHANNEL_BELOW = 1, 2
 
 
 class MsdTensor(ctypes.Structure):
@@ -55,7 +56,7 @@ def _load():
         "msd_block_backward": (i, [i, T, T, i, i, i, ctypes.POINTER(vp), ctypes.POINTER(i), ctypes.POINTER(vp), vp, vp, sz, i, vp]),
         "msd_block_workspace_bytes": (sz, [i, i, i64, i, i, i]),
         "msd_slab_layer_forward": (i, [T, i, vp, vp, i, i, i, vp, sz, i, vp]),
-        "msd_slab_layer_backward": (i, [T, T, i, vp, i, i, i, vp, vp, vp, sz, i, vp]),
+        "msd_slab_layer_backward": (i, [T, T, i, vp, i, i, i, vp, vp, i, vp, sz, i, vp]),
         "msd_tuning_num_variants": (i, [i]),
         "msd_tuning_set": (i, [i, i, i]),
         "msd_tuning_get": (i, [i, i]),

@@ -340,7 +340,8 @@ int msd_slab_layer_forward(const msd_tensor_t *buffer, int n_in, const void *wei
 }
 
 int msd_slab_layer_backward(const msd_tensor_t *result, const msd_tensor_t *gradients, int n_in, const void *weight, int dilation, int z_begin,
-                            int z_end, void *grad_weight, void *grad_bias, void *workspace, size_t workspace_bytes, int device, void *stream) {
+                            int z_end, void *grad_weight, void *grad_bias, int flags, void *workspace, size_t workspace_bytes, int device,
+                            void *stream) {
     View r, gr;
     int rc = slab_checks("msd_slab_layer_backward", result, n_in, dilation, z_begin, z_end, &r);
     if (rc) return rc;
@@ -353,7 +354,12 @@ int msd_slab_layer_backward(const msd_tensor_t *result, const msd_tensor_t *grad
     MSD_CUDA_TRY(g.status);
     View out = channel_slice(r, n_in, 1, 4), in = channel_slice(r, 0, n_in, 4);
     View gout = channel_slice(gr, n_in, 1, 4), gin = channel_slice(gr, 0, n_in, 4);
-    fast::BackwardArgs a{&out, &gout, &in, &gin, (const float *)weight, (float *)grad_weight, (float *)grad_bias, 3, dilation, workspace, workspace_bytes, nullptr, -1};
+    const bool gated_in = (flags & MSD_SLAB_GRADIENT_IS_GATED) != 0;
+    const bool gate_next = (flags & MSD_SLAB_GATE_CHANNEL_BELOW) != 0 && grad_weight != nullptr && n_in >= 2;
+    fast::BackwardArgs a{gated_in ? nullptr : &out, &gout, &in, &gin, (const float *)weight, (float *)grad_weight, (float *)grad_bias, 3, dilation,
+                         workspace, workspace_bytes, nullptr, gate_next ? n_in - 1 : -1};
+    if ((flags & MSD_SLAB_GATE_CHANNEL_BELOW) && !gate_next)
+        MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "msd_slab_layer_backward: MSD_SLAB_GATE_CHANNEL_BELOW needs grad_weight and n_in >= 2");
     if (!fast::backward_supported(a))
         MSD_FAIL(MSD_ERR_UNSUPPORTED, "msd_slab_layer_backward: shape, alignment, dilation or workspace not supported by the tuned 3D kernel");
     fast::set_z_window(z_begin, z_end);

@@ -187,11 +187,18 @@ class SlabBlock:
                                                    self.loc["z_begin"], self.loc["z_end"], self.ws.data_ptr(), self.ws.numel(), dev.index,
                                                    _lib.stream_of(dev)))
 
-    def backward_layer(self, i, weight, dilation, grad_weight, grad_bias_i):
+    def gate_top_channel(self):
+        """Multiply the gradient of the last channel by its ReLU gate on the owned planes (the
+        layers below get theirs gated by the kernel of the layer above)."""
+        g = self.gradients[0, -1, self.owned]
+        g.mul_(self.result[0, -1, self.owned] > 0)
+
+    def backward_layer(self, i, weight, dilation, grad_weight, grad_bias_i, flags=0):
         dev = self.device
         _lib.check(_lib.lib.msd_slab_layer_backward(_lib.describe(self.result), _lib.describe(self.gradients), self.c_in + i, weight.data_ptr(),
                                                     int(dilation), self.loc["z_begin"], self.loc["z_end"], grad_weight.data_ptr(),
-                                                    grad_bias_i.data_ptr(), self.ws.data_ptr(), self.ws.numel(), dev.index, _lib.stream_of(dev)))
+                                                    grad_bias_i.data_ptr(), int(flags), self.ws.data_ptr(), self.ws.numel(), dev.index,
+                                                    _lib.stream_of(dev)))
 
 
 def slab_forward(comm, plan, blocks, weights, bias, dilations):
@@ -212,10 +219,16 @@ def slab_backward(comm, plan, blocks, weights, dilations):
     already summed over the ranks; the input gradient is ``b.gradients[:, :c_in]`` (owned planes)."""
     gws = {r: [torch.zeros_like(w) for w in weights] for r in blocks}
     gbs = {r: torch.zeros(len(weights), device=b.device) for r, b in blocks.items()}
+    # Every layer reads an already gated gradient channel: the top one is gated here, each
+    # other one by the kernel of the layer above when it stores that channel; the exchanged
+    # halo planes therefore carry gated values and no activation halo is read.
+    for b in blocks.values():
+        b.gate_top_channel()
     for i in range(len(weights) - 1, -1, -1):
         comm.exchange(plan, {r: b.gradients[0, b.c_in + i] for r, b in blocks.items()})
+        flags = _lib.SLAB_GRADIENT_IS_GATED | (_lib.SLAB_GATE_CHANNEL_BELOW if i > 0 else 0)
         for r, b in blocks.items():
-            b.backward_layer(i, weights[i], dilations[i], gws[r][i], gbs[r][i:i + 1])
+            b.backward_layer(i, weights[i], dilations[i], gws[r][i], gbs[r][i:i + 1], flags)
     # one sum over the ranks for all weight gradients, one for the bias
     flat = {r: torch.cat([g.reshape(-1) for g in gws[r]] + [gbs[r]]) for r in blocks}
     comm.allreduce_sum(flat)
