@@ -367,11 +367,43 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
                 const float *row = rows + rt * HSLOT + r * TXP + p.Dp;  // row[i] <-> image x = x0 + i
                 const float4 ctr = *reinterpret_cast<const float4 *>(row + 4 * xq);
                 const float cv[4] = {ctr.x, ctr.y, ctr.z, ctr.w};
+                // The x-taps need the 4 consecutive values that start d to the right / left of
+                // the thread's own quad: two aligned 128-bit loads each and a shift by d mod 4
+                // (warp-uniform) instead of four 4-way bank-conflicted scalar loads.
+                const int sh = p.d & 3, qd = p.d >> 2;
+                const float4 *row4 = reinterpret_cast<const float4 *>(row);
+                float up[8], dn[8];
+                {
+                    const float4 l0 = row4[xq + qd], l1 = sh ? row4[xq + qd + 1] : l0;
+                    up[0] = l0.x, up[1] = l0.y, up[2] = l0.z, up[3] = l0.w, up[4] = l1.x, up[5] = l1.y, up[6] = l1.z, up[7] = l1.w;
+                    // values [4xq - d, 4xq - d + 4): quad xq - qd - (sh ? 1 : 0), offset (4 - sh) & 3
+                    const float4 r0 = row4[xq - qd - (sh ? 1 : 0)], r1 = sh ? row4[xq - qd] : r0;
+                    dn[0] = r0.x, dn[1] = r0.y, dn[2] = r0.z, dn[3] = r0.w, dn[4] = r1.x, dn[5] = r1.y, dn[6] = r1.z, dn[7] = r1.w;
+                }
+                float m0v[4], m2v[4];
+                switch (sh) {
+                    case 0:
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) m0v[e] = up[e], m2v[e] = dn[e];
+                        break;
+                    case 1:
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) m0v[e] = up[e + 1], m2v[e] = dn[e + 3];
+                        break;
+                    case 2:
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) m0v[e] = up[e + 2], m2v[e] = dn[e + 2];
+                        break;
+                    default:
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) m0v[e] = up[e + 3], m2v[e] = dn[e + 1];
+                        break;
+                }
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int i = 4 * xq + e;
-                    float m0 = row[i + p.d];
-                    float m2 = row[i - p.d];
+                    float m0 = m0v[e];
+                    float m2 = m2v[e];
                     if (fold_x) {  // block-uniform: only tiles next to the left / right border
                         const int q = x0 + i;
                         const bool f0 = q < p.X && q <= p.d - 1, f2 = q < p.X && q >= p.X - p.d;
