@@ -152,6 +152,27 @@ MSD_API int msd_block_backward(int dtype, const msd_tensor_t *result, const msd_
 /* Scratch bytes `msd_block_backward` needs. */
 MSD_API size_t msd_block_workspace_bytes(int dtype, int ndim, int64_t voxels, int c_in, int depth, int width);
 
+/* ---- final 1x1 layer over the dense buffer ---- */
+
+/* output[n,o,...] = bias[o] + sum_c weight[o,c] * result[n,c,...]: the final layer of the
+ * MSD module (MSDFinalLayer, msd_pytorch/msd_module.py:60-88, a Conv1d on the flattened
+ * buffer in the reference).  float32, at most 8 output channels, unit x-stride and
+ * 16-byte aligned rows; anything else returns MSD_ERR_UNSUPPORTED (the Python layer then
+ * uses a library matrix product). */
+MSD_API int msd_final_forward(int dtype, const msd_tensor_t *result, const void *weight, const void *bias,
+                      const msd_tensor_t *output, int device, void *stream);
+
+/* Backward of the final layer, fused with the set-up of the block backward: WRITES
+ * gradients[n,c,...] = sum_o weight[o,c] * grad_output[n,o,...] for every channel of the
+ * dense gradient buffer (which msd_block_backward then updates in place - the reference's
+ * intermediate gradient tensor and its clone, msd_block.py:83, do not exist here) and
+ * accumulates grad_weight[o,c] and grad_bias[o] (either may be NULL) deterministically.
+ * `workspace`: msd_final_workspace_bytes(). */
+MSD_API int msd_final_backward(int dtype, const msd_tensor_t *result, const msd_tensor_t *grad_output,
+                       const void *weight, const msd_tensor_t *gradients, void *grad_weight, void *grad_bias,
+                       void *workspace, size_t workspace_bytes, int device, void *stream);
+MSD_API size_t msd_final_workspace_bytes(int64_t c_in, int64_t c_out);
+
 /* ---- z-slab decomposition of one 3D volume over several GPUs ---- */
 
 /* No counterpart in the reference (it has no spatial decomposition).  One layer of the

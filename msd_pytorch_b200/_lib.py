@@ -55,6 +55,9 @@ def _load():
         "msd_block_forward": (i, [i, T, i, i, i, ctypes.POINTER(vp), vp, ctypes.POINTER(i), vp, sz, i, vp]),
         "msd_block_backward": (i, [i, T, T, i, i, i, ctypes.POINTER(vp), ctypes.POINTER(i), ctypes.POINTER(vp), vp, vp, sz, i, vp]),
         "msd_block_workspace_bytes": (sz, [i, i, i64, i, i, i]),
+        "msd_final_forward": (i, [i, T, vp, vp, T, i, vp]),
+        "msd_final_backward": (i, [i, T, T, vp, T, vp, vp, vp, sz, i, vp]),
+        "msd_final_workspace_bytes": (sz, [i64, i64]),
         "msd_slab_layer_forward": (i, [T, i, vp, vp, i, i, i, vp, sz, i, vp]),
         "msd_slab_layer_backward": (i, [T, T, i, vp, i, i, i, vp, vp, i, vp, sz, i, vp]),
         "msd_tuning_num_variants": (i, [i]),
@@ -81,6 +84,7 @@ EXPORTED = [
     "msd_conv_backward_k", "msd_conv_relu_backward_k", "msd_conv_backward_bias", "msd_conv_relu_backward_bias",
     "msd_block_forward", "msd_block_backward", "msd_block_workspace_bytes",
     "msd_slab_layer_forward", "msd_slab_layer_backward",
+    "msd_final_forward", "msd_final_backward", "msd_final_workspace_bytes",
     "msd_tuning_num_variants", "msd_tuning_set", "msd_tuning_get",
     "msd_launch_count", "msd_fast_launch_count", "msd_reset_launch_count", "msd_device_status",
     "msd_conv_relu_backward_k_noalloc", "msd_noalloc_scratch_bytes",

@@ -368,6 +368,40 @@ int msd_slab_layer_backward(const msd_tensor_t *result, const msd_tensor_t *grad
     return rc;
 }
 
+size_t msd_final_workspace_bytes(int64_t c_in, int64_t c_out) { return fast::final_workspace_bytes(c_in, c_out); }
+
+int msd_final_forward(int dtype, const msd_tensor_t *result, const void *weight, const void *bias, const msd_tensor_t *output, int device,
+                      void *stream) {
+    View r, o;
+    int nd;
+    int rc = views2("msd_final_forward", result, output, &r, &o, &nd);
+    if (rc) return rc;
+    if (!weight || !bias) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "msd_final_forward: weight and bias must not be null");
+    if (dtype != MSD_F32 || !fast::final_supported(r, o))
+        MSD_FAIL(MSD_ERR_UNSUPPORTED, "msd_final_forward: needs float32, at most 8 output channels, unit x-stride and 16-byte aligned rows");
+    DeviceGuard g(device);
+    MSD_CUDA_TRY(g.status);
+    return fast::final_forward(r, (const float *)weight, (const float *)bias, o, device, (cudaStream_t)stream);
+}
+
+int msd_final_backward(int dtype, const msd_tensor_t *result, const msd_tensor_t *grad_output, const void *weight, const msd_tensor_t *gradients,
+                       void *grad_weight, void *grad_bias, void *workspace, size_t workspace_bytes, int device, void *stream) {
+    View r, go, gr;
+    int nd;
+    int rc = views2("msd_final_backward", result, grad_output, &r, &go, &nd);
+    if (rc) return rc;
+    if ((rc = views2("msd_final_backward", result, gradients, &r, &gr, &nd))) return rc;
+    if (gr.c != r.c) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "msd_final_backward: gradients and result differ in channels");
+    if (!weight) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "msd_final_backward: weight must not be null");
+    if (workspace && ((uintptr_t)workspace & 255)) MSD_FAIL(MSD_ERR_WORKSPACE, "msd_final_backward: workspace must be 256-byte aligned");
+    if (dtype != MSD_F32 || !fast::final_supported(r, go) || !fast::final_supported(gr, go))
+        MSD_FAIL(MSD_ERR_UNSUPPORTED, "msd_final_backward: needs float32, at most 8 output channels, unit x-stride and 16-byte aligned rows");
+    DeviceGuard g(device);
+    MSD_CUDA_TRY(g.status);
+    return fast::final_backward(r, go, (const float *)weight, gr, (float *)grad_weight, (float *)grad_bias, workspace, workspace_bytes, device,
+                                (cudaStream_t)stream);
+}
+
 int msd_tuning_num_variants(int family) { return fast::num_variants(family); }
 int msd_tuning_set(int family, int dilation, int variant) { return fast::tuning_set(family, dilation, variant); }
 int msd_tuning_get(int family, int dilation) { return fast::tuning_get(family, dilation); }

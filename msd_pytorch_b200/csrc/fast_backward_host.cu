@@ -123,21 +123,22 @@ struct ReduceTable {
 __global__ void __launch_bounds__(128) reduce_table_kernel(const __grid_constant__ ReduceTable t) {
     const ReduceEntry &e = t.e[blockIdx.y];
     const int j = blockIdx.x * 128 + threadIdx.x;
-    const int nk = e.pk ? e.nk : 0;
+    const int nk = (e.pk && e.gk) ? e.nk : 0;
+    const int64_t pitch = e.pitch ? e.pitch : nk, pitch_b = e.pitch_b ? e.pitch_b : 1;
     if (j < nk) {
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
         int q = 0;
         for (; q + 3 < e.nparts; q += 4) {
-            s0 += e.pk[(int64_t)(q + 0) * nk + j];
-            s1 += e.pk[(int64_t)(q + 1) * nk + j];
-            s2 += e.pk[(int64_t)(q + 2) * nk + j];
-            s3 += e.pk[(int64_t)(q + 3) * nk + j];
+            s0 += e.pk[(int64_t)(q + 0) * pitch + j];
+            s1 += e.pk[(int64_t)(q + 1) * pitch + j];
+            s2 += e.pk[(int64_t)(q + 2) * pitch + j];
+            s3 += e.pk[(int64_t)(q + 3) * pitch + j];
         }
-        for (; q < e.nparts; ++q) s0 += e.pk[(int64_t)q * nk + j];
+        for (; q < e.nparts; ++q) s0 += e.pk[(int64_t)q * pitch + j];
         e.gk[j] += (s0 + s1) + (s2 + s3);
-    } else if (j == nk && e.pb) {
+    } else if (j == nk && e.pb && e.gb) {
         float s0 = 0.f;
-        for (int q = 0; q < e.nparts; ++q) s0 += e.pb[q];
+        for (int q = 0; q < e.nparts; ++q) s0 += e.pb[(int64_t)q * pitch_b];
         e.gb[0] += s0;
     }
 }
@@ -148,7 +149,7 @@ int flush_reductions(ReduceList *list, cudaStream_t s) {
     int max_n = 1;
     for (int i = 0; i < list->count; ++i) {
         t.e[i] = list->e[i];
-        const int n = (list->e[i].pk ? list->e[i].nk : 0) + 1;
+        const int n = ((list->e[i].pk && list->e[i].gk) ? list->e[i].nk : 0) + 1;
         if (n > max_n) max_n = n;
     }
     dim3 grid((unsigned)ceil_div(max_n, 128), (unsigned)list->count);
@@ -295,6 +296,7 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
         if (!a.defer) single.count = 0, single.ws_used = 0;
         ReduceEntry &e = list->e[list->count++];
         e.pk = p.part_k, e.pb = p.part_b, e.gk = a.gk, e.gb = a.gb, e.nparts = grid, e.nk = (int)(C * taps);
+        e.pitch = 0, e.pitch_b = 0;
         list->ws_used += need;
         if (!a.defer && (rc = flush_reductions(list, s))) return rc;
     }

@@ -44,6 +44,8 @@ struct ReduceEntry {
     float *gk;        // accumulated into
     float *gb;        // accumulated into
     int nparts, nk;
+    int64_t pitch;    // elements between consecutive partial rows of pk (0: nk)
+    int64_t pitch_b;  // elements between consecutive partials of pb (0: 1)
 };
 struct ReduceList {
     static const int kMax = 64;
@@ -79,6 +81,13 @@ int gate_channel(const View &g, const View &a, int device, cudaStream_t s);
 bool backward_supported(const BackwardArgs &a);
 size_t backward_workspace_bytes(int nd, int64_t c_in);
 int backward(const BackwardArgs &a, int device, cudaStream_t s);
+
+// Final 1x1 layer over the dense buffer (float32, up to 8 output channels, aligned views).
+bool final_supported(const View &res, const View &out);
+size_t final_workspace_bytes(int64_t c_in, int64_t c_out);
+int final_forward(const View &res, const float *w, const float *bias, const View &out, int device, cudaStream_t s);
+int final_backward(const View &res, const View &gout, const float *w, const View &grad, float *gw, float *gb, void *ws, size_t wsb, int device,
+                   cudaStream_t s);
 
 }  // namespace fast
 }  // namespace msd

@@ -5,7 +5,8 @@ from math import sqrt
 import numpy as np
 import torch
 
-from .msd_block import MSDBlock
+from . import _lib
+from .msd_block import MSDBlock, _voxels, block_backward_, block_forward_
 
 DEFAULT_DILATIONS = [1, 2, 3, 4, 5, 6, 7, 8, 9, 10]
 
@@ -50,6 +51,67 @@ class MSDFinalLayer(torch.nn.Module):
         self.linear.bias.data.zero_()
 
 
+def _final_kernels_apply(result, c_out):
+    """The fused final-layer kernels take float32 CUDA buffers with 16-byte aligned rows and
+    at most 8 output channels."""
+    return result.is_cuda and result.dtype == torch.float32 and c_out <= 8 and result.shape[-1] % 4 == 0 and result.is_contiguous()
+
+
+class MSDModuleFunction(torch.autograd.Function):
+    """Dense block + final 1x1 layer as ONE autograd node.
+
+    Same arithmetic as ``MSDFinalLayer(msd_block(input, ...))`` (msd_module.py:144-147 of the
+    reference).  What the fusion removes is data movement: the final layer's backward writes
+    the gradient of every channel straight into the buffer that the block backward updates
+    in place, so the dense gradient tensor that autograd would pass between the two nodes,
+    and the copy of it that the block backward must take (msd_block.py:83), never exist."""
+
+    @staticmethod
+    def forward(ctx, input, dilations, bias, final_weight, final_bias, *weights):
+        depth = len(dilations)
+        assert depth == len(weights), "number of weights does not match depth"
+        c_in = input.shape[1]
+        c_total = c_in + sum(w.shape[0] for w in weights)
+        c_out = final_weight.shape[0]
+        result = input.new_empty(input.shape[0], c_total, *input.shape[2:])
+        result[:, :c_in] = input
+        block_forward_(result, c_in, list(dilations), bias.contiguous(), [w.detach() for w in weights])
+        out = input.new_empty(input.shape[0], c_out, *input.shape[2:])
+        dev = input.device
+        fw = final_weight.detach().reshape(c_out, c_total).contiguous()
+        _lib.check(_lib.lib.msd_final_forward(_lib.MSD_F32, _lib.describe(result), fw.data_ptr(), final_bias.detach().contiguous().data_ptr(),
+                                              _lib.describe(out), dev.index, _lib.stream_of(dev)))
+        ctx.dilations = list(dilations)
+        ctx.c_in = c_in
+        ctx.save_for_backward(bias, result, final_weight, *weights)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        bias, result, final_weight, *weights = ctx.saved_tensors
+        dev = result.device
+        c_out, c_total = final_weight.shape[0], result.shape[1]
+        grad_out = grad_out.contiguous()
+        gradients = torch.empty_like(result)
+        fw = final_weight.detach().reshape(c_out, c_total).contiguous()
+        gfw = torch.zeros_like(fw)
+        gfb = torch.zeros(c_out, dtype=result.dtype, device=dev)
+        ws = _lib.workspace(dev, _lib.lib.msd_final_workspace_bytes(c_total, c_out))
+        _lib.check(_lib.lib.msd_final_backward(_lib.MSD_F32, _lib.describe(result), _lib.describe(grad_out), fw.data_ptr(), _lib.describe(gradients),
+                                               gfw.data_ptr(), gfb.data_ptr(), ws.data_ptr(), ws.numel(), dev.index, _lib.stream_of(dev)))
+        # one zero-filled buffer for all weight gradients (a single fill instead of one per layer)
+        sizes = [w.numel() for w in weights]
+        flat = torch.zeros(sum(sizes), dtype=result.dtype, device=dev)
+        grad_weights, off = [], 0
+        for w, n in zip(weights, sizes):
+            grad_weights.append(flat[off:off + n].view_as(w) if ctx.needs_input_grad[5 + len(grad_weights)] else None)
+            off += n
+        grad_bias = torch.zeros_like(bias) if ctx.needs_input_grad[2] else None
+        block_backward_(result, gradients, ctx.c_in, ctx.dilations, [w.detach() for w in weights], grad_weights, grad_bias)
+        grad_input = gradients[:, :ctx.c_in] if ctx.needs_input_grad[0] else None
+        return (grad_input, None, grad_bias, gfw.view_as(final_weight), gfb, *grad_weights)
+
+
 class MSDModule(torch.nn.Module):
     """``MSDModule(c_in, c_out, depth, width, dilations, ndim)``: ``dilations`` is
     repeated cyclically over the ``depth`` layers."""
@@ -76,4 +138,9 @@ class MSDModule(torch.nn.Module):
         self.final_layer.reset_parameters()
 
     def forward(self, input):
-        return self.final_layer(self.msd_block(input))
+        blk = self.msd_block
+        if input.dim() in (4, 5) and _final_kernels_apply(input, self.c_out) and input.shape[-1] * 4 % 16 == 0:
+            weights = (getattr(blk, "weight{}".format(i)) for i in range(len(blk.weights)))
+            return MSDModuleFunction.apply(input.contiguous(), blk.dilations, blk.bias, self.final_layer.linear.weight,
+                                           self.final_layer.linear.bias, *weights)
+        return self.final_layer(blk(input))

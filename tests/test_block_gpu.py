@@ -242,3 +242,49 @@ def test_reference_python_layers_run_on_this_backend(cuda_device):
     again.conv_relu_forward(x, torch.randn(1, 2, 3, 3, device=dev), torch.zeros(1, device=dev), y, 2, block_size=(0, 16, 16))
     torch.cuda.synchronize()
     assert torch.isfinite(y).all()
+
+
+@pytest.mark.parametrize("nd,depth,B,sp,c_out", [(2, 10, 2, (64, 96), 1), (2, 6, 2, (40, 72), 4), (3, 6, 1, (12, 24, 40), 3)],
+                         ids=["2d_regression", "2d_4_classes", "3d_3_outputs"])
+def test_fused_module_matches_oracle_and_unfused(cuda_device, nd, depth, B, sp, c_out):
+    """MSDModule (block + final 1x1 layer as one autograd node, gradients written in place)
+    against the float64 CPU oracle and against the unfused composition of the same modules."""
+    from oracle import msd_oracle as O
+    from msd_pytorch_b200.msd_module import MSDModule, MSDModuleFunction
+
+    dev = cuda_device
+    x, ws, bias, fw, fb, dil, g = _network_case(nd, depth, B, sp, c_out, 77)
+    target = torch.randn(B, c_out, *sp, generator=g)
+    loss_o, res_o, gi_o, gb_o, gws_o, gfw_o, gfb_o = O.msd_network_step(
+        x.double(), target.double(), dil, bias.double(), [w.double() for w in ws], fw.double(), fb.double(), "mse")
+    net = MSDModule(1, c_out, depth, 1, dilations=dil, ndim=nd).to(dev)
+    with torch.no_grad():
+        for i, w in enumerate(ws):
+            getattr(net.msd_block, "weight%d" % i).copy_(w)
+        net.msd_block.bias.copy_(bias)
+        net.final_layer.linear.weight.copy_(fw.unsqueeze(-1))
+        net.final_layer.linear.bias.copy_(fb)
+    xd = x.to(dev).requires_grad_(True)
+    out = net(xd)
+    assert isinstance(out.grad_fn, MSDModuleFunction._backward_cls) or "MSDModuleFunction" in type(out.grad_fn).__name__
+    loss = torch.nn.functional.mse_loss(out, target.to(dev))
+    loss.backward()
+    torch.cuda.synchronize()
+    assert abs(loss.item() - loss_o.item()) <= 1e-4 * abs(loss_o.item())
+    assert_close(xd.grad, gi_o, 1e-3, "grad_input")
+    assert_close(net.msd_block.bias.grad, gb_o, 1e-3, "grad_bias")
+    assert_close(net.final_layer.linear.weight.grad.squeeze(-1), gfw_o, 1e-3, "grad_final_weight")
+    assert_close(net.final_layer.linear.bias.grad, gfb_o, 1e-3, "grad_final_bias")
+    for i, gw_o in enumerate(gws_o):
+        assert_close(getattr(net.msd_block, "weight%d" % i).grad, gw_o, 1e-3, "grad_weight%d" % i)
+    # unfused composition of the same modules
+    fused = [p.grad.clone() for p in net.parameters()]
+    for p in net.parameters():
+        p.grad = None
+    x2 = x.to(dev).requires_grad_(True)
+    out2 = net.final_layer(net.msd_block(x2))
+    torch.nn.functional.mse_loss(out2, target.to(dev)).backward()
+    assert_close(out, out2, 1e-5, "fused vs unfused output")
+    assert_close(xd.grad, x2.grad, 1e-4, "fused vs unfused grad_input")
+    for a, p in zip(fused, net.parameters()):
+        assert_close(a, p.grad, 1e-4, "fused vs unfused parameter gradient")
