@@ -54,12 +54,12 @@ def algorithmic_bytes(depth, voxels):
 
 
 # DRAM traffic per launch measured by ncu (dram__bytes_read.sum + dram__bytes_write.sum) divided
-# by the algorithmic bytes of the captured launch: 2D backward 1234.1 / 1275.1 MB and 2D forward
-# 433.0 / 427.8 MB (batch 8 of 512x512, 50 input channels, dilation 10); 3D backward
-# 1254.8 / 1291.8 MB and 3D forward 509.7 / 436.2 MB (batch 2 of 128^3, 25 input channels,
+# by the algorithmic bytes of the captured launch: 2D backward 1224.7 / 1275.1 MB and 2D forward
+# 429.6 / 427.8 MB (batch 8 of 512x512, 50 input channels, dilation 10); 3D backward
+# 1238.4 / 1291.8 MB and 3D forward 509.6 / 436.2 MB (batch 2 of 128^3, 25 input channels,
 # dilation 4).  Traffic grows with the channel count like the algorithmic bytes do, so the ratio
 # is applied to the average launch.
-NCU_TRAFFIC_RATIO = {("bwd", 2): 1234.1 / 1275.1, ("fwd", 2): 433.0 / 427.8, ("bwd", 3): 1254.8 / 1291.8, ("fwd", 3): 509.7 / 436.2}
+NCU_TRAFFIC_RATIO = {("bwd", 2): 1224.7 / 1275.1, ("fwd", 2): 429.6 / 427.8, ("bwd", 3): 1238.4 / 1291.8, ("fwd", 3): 509.6 / 436.2}
 
 
 def measured_peak():
