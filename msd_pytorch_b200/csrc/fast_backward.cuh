@@ -217,7 +217,11 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
     if (DO_K) {
         for (int i = tid; i < kConsumerWarps * p.C * TAPS_PAD; i += kBwdThreads) wacc[i] = 0.f;
     }
+    tma::allow_dependents();
     __syncthreads();
+    // everything above only touched this layer's constants; the gradient channels below were
+    // written by the kernel of the layer above
+    tma::grid_dependency_wait();
 
     const long long tiles_per_plane = (long long)p.tiles_x * p.tiles_y;
 

@@ -8,8 +8,7 @@ template <int TXQ, int J, bool DO_X, bool DO_K>
 static int launch2d(const CUtensorMap *m, const BwdParams &p, int grid, size_t smem, cudaStream_t s) {
     auto kern = fused_backward_kernel<2, TXQ, J, DO_X, DO_K>;
     MSD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, bwd_consumer_warps(2) * 32 + 32, smem, s>>>(m[0], m[1], m[2], m[3], p);
-    MSD_CUDA_TRY(cudaGetLastError());
+    MSD_CUDA_TRY(tma::launch_pdl(kern, dim3(grid), dim3(bwd_consumer_warps(2) * 32 + 32), smem, s, m[0], m[1], m[2], m[3], p));
     return MSD_OK;
 }
 

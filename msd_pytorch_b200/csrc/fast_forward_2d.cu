@@ -90,8 +90,7 @@ static int launch_fwd2d(const CUtensorMap &map, const Fwd2dParams &p, int grid, 
     auto kern = forward2d_kernel<D, R, Q, K, NT, TW>;
     const size_t smem = 256 + (size_t)stages * Cfg::STAGE_BYTES + (size_t)((p.C * (NT == 3 ? 28 : 12) + 31) & ~31) * 4;
     MSD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, Cfg::THREADS, smem, s>>>(map, p);
-    MSD_CUDA_TRY(cudaGetLastError());
+    MSD_CUDA_TRY(tma::launch_pdl(kern, dim3(grid), dim3(Cfg::THREADS), smem, s, map, p));
     return MSD_OK;
 }
 

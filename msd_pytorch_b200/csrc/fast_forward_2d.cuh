@@ -149,7 +149,11 @@ forward2d_kernel(const __grid_constant__ CUtensorMap map, const Fwd2dParams p) {
         const int c = i / WP, t = i % WP;
         wsm[i] = (c < p.C && t < NT * 9) ? p.k[c * NT * 9 + t] : 0.f;
     }
+    tma::allow_dependents();
     __syncthreads();
+    // everything above only touched this layer's constants; the channels below were written by
+    // the previous layer's kernel
+    tma::grid_dependency_wait();
 
     const long long tiles_per_image = (long long)p.tiles_x * p.tiles_y;
 

@@ -9,6 +9,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <utility>
 
 namespace msd {
 namespace tma {
@@ -96,6 +97,31 @@ __device__ __forceinline__ void tensor_g2s_5d(void *dst_smem, const CUtensorMap 
 
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialisation
+// attribute may start while the previous kernel of the stream is still draining: everything
+// before grid_dependency_wait() (barrier set-up, staging of the layer's weights) overlaps the
+// predecessor's tail; nothing the predecessor wrote may be touched before it.
+// allow_dependents() tells the scheduler that the NEXT kernel's blocks may be placed as soon
+// as resources free up.  Both are no-ops for kernels launched the ordinary way.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void allow_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Host: launch `kernel` on `s` with programmatic stream serialisation.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
 // Named barrier among `count` threads (count a multiple of 32); id 1..15.
