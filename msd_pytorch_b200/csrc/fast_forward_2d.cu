@@ -32,27 +32,41 @@ struct MapKey {
 struct MapEntry {
     MapKey key;
     CUtensorMap map;
-    uint64_t stamp;
+    bool used;
 };
+// Open-addressing hash table.  A block forward + backward of depth 100 touches about 500
+// distinct descriptors (the channel count and the base pointer of the single-channel views
+// change per layer); when the table is three quarters full it is simply emptied.
+static const int kMapSlots = 4096;
 static std::mutex g_map_mu;
-static MapEntry g_maps[128];
+static MapEntry *g_maps = nullptr;
 static int g_map_count = 0;
-static uint64_t g_map_clock = 0;
+
+static uint64_t hash_key(const MapKey &k) {
+    const unsigned char *b = reinterpret_cast<const unsigned char *>(&k);
+    uint64_t h = 1469598103934665603ull;
+    for (size_t i = 0; i < sizeof(MapKey); ++i) h = (h ^ b[i]) * 1099511628211ull;
+    return h;
+}
 
 // Tiled descriptor over a float32 tensor; dims/strides innermost first, strides in elements
-// (strides[0] must be 1).  Entries are cached, least recently used first out.
+// (strides[0] must be 1).  Descriptors are cached by (device, pointer, geometry, box).
 int get_tensor_map(int device, const void *ptr, int rank, const int64_t *dims, const int64_t *strides, const int *box, CUtensorMap *out) {
     MapKey key;
     memset(&key, 0, sizeof(key));
     key.ptr = ptr, key.rank = rank, key.device = device;
     for (int i = 0; i < rank; ++i) key.dims[i] = dims[i], key.strides[i] = strides[i], key.box[i] = box[i];
+    const uint64_t h = hash_key(key);
     std::lock_guard<std::mutex> l(g_map_mu);
-    for (int i = 0; i < g_map_count; ++i)
-        if (g_maps[i].key == key) {
-            g_maps[i].stamp = ++g_map_clock;
-            *out = g_maps[i].map;
+    if (!g_maps) g_maps = new MapEntry[kMapSlots]();
+    int slot = (int)(h & (kMapSlots - 1));
+    while (g_maps[slot].used) {
+        if (g_maps[slot].key == key) {
+            *out = g_maps[slot].map;
             return MSD_OK;
         }
+        slot = (slot + 1) & (kMapSlots - 1);
+    }
     PFN_cuTensorMapEncodeTiled_v12000 enc = get_encode();
     if (!enc) MSD_FAIL(MSD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t gdim[5], gstr[4];
@@ -68,17 +82,15 @@ int get_tensor_map(int device, const void *ptr, int rank, const int64_t *dims, c
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) MSD_FAIL(MSD_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
-    int slot = g_map_count;
-    if (g_map_count < 128) {
-        ++g_map_count;
-    } else {
-        slot = 0;
-        for (int i = 1; i < 128; ++i)
-            if (g_maps[i].stamp < g_maps[slot].stamp) slot = i;
+    if (g_map_count >= kMapSlots * 3 / 4) {
+        memset(g_maps, 0, sizeof(MapEntry) * kMapSlots);
+        g_map_count = 0;
+        slot = (int)(h & (kMapSlots - 1));
     }
     g_maps[slot].key = key;
     g_maps[slot].map = m;
-    g_maps[slot].stamp = ++g_map_clock;
+    g_maps[slot].used = true;
+    ++g_map_count;
     *out = m;
     return MSD_OK;
 }

@@ -2,7 +2,7 @@
 //
 // These are the always-correct path: float32 and float64, arbitrary strides,
 // any number of input and output channels, any size >= dilation.  The tuned
-// sm_100a kernels in fast2d_forward.cu / fast_backward.cu take over for the
+// sm_100a kernels in fast_forward_2d.cuh / fast_backward.cuh take over for the
 // float32, width-1 shapes of the MSD block; everything else lands here.
 //
 // Arithmetic contract (what the reference's kernels compute):
