@@ -1,0 +1,451 @@
+// Fused backward of one 3D MSD layer (one output channel, float32) with the consumer warps
+// split by role.  Same mathematics and buffers as fused_backward_kernel (fast_backward.cuh);
+// what differs is who computes what:
+//
+//   X warps  voxels across lanes (4 consecutive x per thread), the 27 values M_t of each
+//            voxel in registers: per channel 27 x 4 FMAs update the input gradient, one
+//            128-bit store.  No reduction of any kind.
+//   K warps  the 27 TAPS across lanes: lane t keeps M_t[v] for the 64 voxels v of half a tile
+//            row in registers and reads in[c][v] with broadcast 128-bit shared loads, so
+//            that it accumulates  sum_v in[c][v] * M_t[v]  all by itself.  The weight gradient
+//            needs NO cross-lane reduction (the shuffle reduce-scatter of the unsplit kernel
+//            costs 124 instructions per 216 FMAs in 3D); lanes 27..31 idle.
+//
+// A tile is 4 rows x 128 columns of one z-plane.  The block has four warpgroups:
+//   warps 0-3    X warps, one per tile row               (registers raised to kSplitRegsX)
+//   warps 4-11   K warps, (row, half) = (w-4)/2, (w-4)%2 (the launch's 128 registers)
+//   warp 12      TMA producer; warps 13-15 exit at once  (registers lowered to kSplitRegsP)
+// so that each of the four warp schedulers (warp id mod 4) carries one X warp and two K warps.
+// The register file is re-divided between the warpgroups with setmaxnreg: the X warps need
+// 108 registers for M alone, the producer next to none.
+//
+// Data movement.  One ring stage holds kSplitCB consecutive channels of the tile: two TMA
+// boxes (activations, gradients) of kSplitCB x 4 x 128 floats, so that the cost of issuing a
+// copy and of the full/empty hand-shake is paid once per kSplitCB channels.  The 9 halo row
+// groups of gout (and of out, for the ReLU gate) land by TMA.  The consumers turn them into
+// the table  Msm[t][row][x] = M_t(voxel)  in two short cooperative passes (gate + y/z folds in
+// place; x shifts + x folds into the table) and both kinds of warps then fill their registers
+// with aligned 128-bit loads and no arithmetic.  The table's tap stride is 4 mod 32 banks,
+// which makes the K warps' lane-per-tap loads conflict-free.
+//
+// Requirements (checked by the host): X a multiple of 128, dilation <= 12, both gradients wanted.
+#pragma once
+#include "fast_backward.cuh"
+
+namespace msd {
+namespace fast {
+
+constexpr int kSplitRows = 4;
+constexpr int kSplitTX = 128;
+constexpr int kSplitCB = 4;                                       // channels per ring stage
+constexpr int kSplitKHalf = 64;                                   // voxels per K warp
+constexpr int kSplitXWarps = kSplitRows;
+constexpr int kSplitKWarps = 2 * kSplitRows;
+constexpr int kSplitConsumerWarps = kSplitXWarps + kSplitKWarps;  // 12
+constexpr int kSplitConsumers = kSplitConsumerWarps * 32;         // 384
+constexpr int kSplitThreads = 512;                                // four warpgroups
+constexpr int kSplitWaccPad = 28;                                 // floats per (K warp, channel) slot
+constexpr int kSplitWPad = 28;                                    // floats per channel of weights in shared memory
+constexpr int kSplitMaxD = 12;                                    // border columns handled per side
+constexpr int kSplitMaxStages = 8;
+constexpr int kSplitHeaderBytes = 512;                            // barriers, abort flag, bias slots
+constexpr int kSplitRegsX = 176, kSplitRegsP = 24;
+
+// Bounded wait with a fast path: one try_wait before the generic bounded loop.
+__device__ __forceinline__ void split_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
+    if (tma::mbar_try_wait(bar, parity)) return;
+    tma::wait_parity(bar, parity, abort_flag, status, code);
+}
+
+// Pass A: turns the halo rows of one tile (landed by TMA in `rows` / `orows`, slots of HSLOT
+// floats) into the rows of m, in place: ReLU gate, plus the mirrored y / z sources next to
+// the volume's borders.  Cooperative over the kSplitConsumers consumer threads; the caller
+// synchronises them afterwards.
+__device__ __forceinline__ void split_fill_rows(const BwdParams &p, float *rows, const float *orows, int HSLOT, int TXP, bool gate, int ctid, int n,
+                                                int z, int y0, int x0) {
+    constexpr int RT = 9, TR = kSplitRows;
+    const bool fold_rows = (y0 < p.d) || (y0 + TR + p.d > p.Y) || (z < p.d || z + p.d >= p.Z);
+    if (!gate && !fold_rows) return;
+    const float *go_n = p.gout + n * p.go_sn;
+    const float *out_n = gate ? p.out + n * p.out_sn : nullptr;
+    const int quads = TXP / 4;
+    for (int item = ctid; item < RT * TR * quads; item += kSplitConsumers) {
+        const int rowid = item / quads, q4 = item - rowid * quads;
+        const int rt = rowid / TR, rr = rowid - rt * TR;
+        const int soff = rt * HSLOT + rr * TXP + 4 * q4;
+        float4 g = *reinterpret_cast<const float4 *>(rows + soff);
+        if (gate) {
+            const float4 o = *reinterpret_cast<const float4 *>(orows + soff);
+            g.x = o.x > 0.f ? g.x : 0.f;
+            g.y = o.y > 0.f ? g.y : 0.f;
+            g.z = o.z > 0.f ? g.z : 0.f;
+            g.w = o.w > 0.f ? g.w : 0.f;
+        }
+        if (fold_rows) {
+            const int y = y0 + rr, px = x0 - p.Dp + 4 * q4;
+            int zs[2], ys[2], nys = 0;
+            const int nzs = adjoint_sources_dev(z, rt / 3, p.d, p.Z, zs);
+            if (y < p.Y && nzs > 0) nys = adjoint_sources_dev(y, rt % 3, p.d, p.Y, ys);
+            if (px >= 0 && px < p.X && nzs * nys > 0) {
+                const int dy = y - p.d * (rt % 3 - 1), dz = z - p.d * (rt / 3 - 1);
+                for (int a = 0; a < nzs; ++a)
+                    for (int b = 0; b < nys; ++b) {
+                        if (ys[b] == dy && zs[a] == dz) continue;  // the TMA box already holds it
+                        float4 g2 = ld4(go_n + zs[a] * p.go_sz + (int64_t)ys[b] * p.go_sy + px);
+                        if (out_n) {
+                            const float4 o2 = ld4(out_n + zs[a] * p.out_sz + (int64_t)ys[b] * p.out_sy + px);
+                            g2.x = o2.x > 0.f ? g2.x : 0.f;
+                            g2.y = o2.y > 0.f ? g2.y : 0.f;
+                            g2.z = o2.z > 0.f ? g2.z : 0.f;
+                            g2.w = o2.w > 0.f ? g2.w : 0.f;
+                        }
+                        g.x += g2.x, g.y += g2.y, g.z += g2.z, g.w += g2.w;
+                    }
+            }
+        }
+        *reinterpret_cast<float4 *>(rows + soff) = g;
+    }
+}
+
+// Pass B: the table  msm[t * TS + row * 128 + i] = M_t at voxel (row, x0 + i),  t = (tz, ty, tx):
+// the row of m that tap (tz, ty) reads, shifted by -d (tx - 1) columns, plus the mirrored x
+// source next to the left (tx = 0) / right (tx = 2) border of the image.
+__device__ __forceinline__ void split_build_table(const BwdParams &p, const float *rows, float *msm, int HSLOT, int TXP, int TS, int ctid, int x0) {
+    constexpr int TAPS = 27, TR = kSplitRows, TX = kSplitTX;
+    const bool fold_l = x0 == 0, fold_r = x0 + TX == p.X;
+#pragma unroll 3
+    for (int item = ctid; item < TAPS * TR * (TX / 4); item += kSplitConsumers) {
+        const int xq = item & 31, rr = (item >> 5) & 3, t = item >> 7;
+        const int rt = t / 3, tx = t - 3 * rt;
+        const float *row = rows + rt * HSLOT + rr * TXP + p.Dp;  // row[i] <-> image x = x0 + i
+        const int i0 = 4 * xq;
+        float4 v;
+        if (tx == 1) {
+            v = *reinterpret_cast<const float4 *>(row + i0);
+        } else {
+            const float *src = row + i0 - p.d * (tx - 1);
+            v = make_float4(src[0], src[1], src[2], src[3]);
+            if (tx == 0 && fold_l && i0 < p.d) {  // columns q <= d - 1 also get the source d - 1 - q
+                v.x += row[p.d - 1 - i0];
+                if (i0 + 1 < p.d) v.y += row[p.d - 2 - i0];
+                if (i0 + 2 < p.d) v.z += row[p.d - 3 - i0];
+                if (i0 + 3 < p.d) v.w += row[p.d - 4 - i0];
+            }
+            if (tx == 2 && fold_r && i0 + 3 >= TX - p.d) {  // columns q >= X - d also get 2X - 1 - q - d
+                const int b = 2 * TX - 1 - p.d - i0;         // local source column of element 0
+                if (i0 + 0 >= TX - p.d) v.x += row[b];
+                if (i0 + 1 >= TX - p.d) v.y += row[b - 1];
+                if (i0 + 2 >= TX - p.d) v.z += row[b - 2];
+                v.w += row[b - 3];
+            }
+        }
+        *reinterpret_cast<float4 *>(msm + t * TS + rr * TX + i0) = v;
+    }
+}
+
+__global__ void __launch_bounds__(kSplitThreads, 1)
+fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_gin,
+                              const __grid_constant__ CUtensorMap map_gout, const __grid_constant__ CUtensorMap map_out, const BwdParams p) {
+    constexpr int RT = 9, TAPS = 27;
+    constexpr int TX = kSplitTX, TR = kSplitRows, KH = kSplitKHalf, CB = kSplitCB;
+    constexpr int CHAN = TR * TX;        // floats of one channel of one tensor in a stage
+    constexpr int STAGE = 2 * CB * CHAN;  // CB channels of in, then CB channels of gin
+
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw);
+    uint64_t *empty = full + kSplitMaxStages;
+    uint64_t *halo_full = empty + kSplitMaxStages;  // the halo rows of a tile have landed
+    uint64_t *halo_empty = halo_full + 1;           // ... have been turned into the table: the slots are free
+    uint64_t *m_done = halo_empty + 1;              // every consumer warp has its M registers: the table is free
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(m_done + 1);
+    float *red = reinterpret_cast<float *>(smem_raw + 384);
+    const int TXP = TX + 2 * p.Dp;
+    const bool gate = p.out != nullptr;
+    float *rows = reinterpret_cast<float *>(smem_raw + kSplitHeaderBytes);
+    const int HSLOT = (TR * TXP + 31) & ~31;
+    constexpr int TS = TR * TX + 4;  // tap stride of the table: 4 banks apart
+    float *orows = rows + RT * HSLOT;
+    float *msm = orows + (gate ? RT * HSLOT : 0);
+    float *ring = msm + ((TAPS * TS + 31) & ~31);
+    float *wsm = ring + (size_t)p.stages * STAGE;
+    float *wacc = wsm + p.C * kSplitWPad;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int S = p.stages;
+    const int ngroups = (p.C + CB - 1) / CB;
+
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) {
+            tma::mbar_init(&full[s], 1);
+            tma::mbar_init(&empty[s], kSplitConsumerWarps);
+        }
+        tma::mbar_init(halo_full, 1);
+        tma::mbar_init(halo_empty, 1);
+        tma::mbar_init(m_done, kSplitConsumerWarps);
+        *abort_flag = 0;
+        tma::fence_barrier_init();
+    }
+    for (int i = tid; i < p.C * kSplitWPad; i += kSplitThreads) {
+        const int c = i / kSplitWPad, t = i % kSplitWPad;
+        wsm[i] = t < TAPS ? p.k[c * TAPS + t] : 0.f;
+    }
+    for (int i = tid; i < kSplitKWarps * p.C * kSplitWaccPad; i += kSplitThreads) wacc[i] = 0.f;
+    tma::allow_dependents();
+    __syncthreads();
+    tma::grid_dependency_wait();
+
+    const long long tiles_per_plane = (long long)p.tiles_x * p.tiles_y;
+
+    if (warp >= kSplitConsumerWarps) {
+        // ------------------- producer warpgroup: warp 12 issues, 13-15 leave -------------------
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kSplitRegsP));
+        if (warp == kSplitConsumerWarps && lane == 0) {
+            tma::prefetch_tensormap(&map_in);
+            tma::prefetch_tensormap(&map_gin);
+            tma::prefetch_tensormap(&map_gout);
+            if (gate) tma::prefetch_tensormap(&map_out);
+            const uint32_t halo_bytes = (uint32_t)(RT * TR * TXP * 4) * (gate ? 2u : 1u);
+            auto issue_halo = [&](long long tile) {
+                const int tx_i = (int)(tile % p.tiles_x);
+                const int ty_i = (int)((tile / p.tiles_x) % p.tiles_y);
+                const long long nz = tile / tiles_per_plane;
+                const int z = p.z0 + (int)(nz % p.ZW), n = (int)(nz / p.ZW);
+                const int bx = tx_i * TX - p.Dp, y0 = ty_i * TR;
+                tma::mbar_arrive_expect_tx(halo_full, halo_bytes);
+#pragma unroll 1
+                for (int rt = 0; rt < RT; ++rt) {
+                    const int by = y0 + p.d * (1 - rt % 3), bz = z + p.d * (1 - rt / 3);
+                    tma::tensor_g2s_5d(rows + rt * HSLOT, &map_gout, bx, by, bz, 0, n, halo_full);
+                    if (gate) tma::tensor_g2s_5d(orows + rt * HSLOT, &map_out, bx, by, bz, 0, n, halo_full);
+                }
+            };
+            uint32_t it = 0, tcount = 0, s = 0, ph = 0;
+            if ((long long)blockIdx.x < p.num_tiles) issue_halo(blockIdx.x);
+            const int halo_at = (ngroups < S ? ngroups : S) - 1;
+            for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++tcount) {
+                const int tx_i = (int)(tile % p.tiles_x);
+                const int ty_i = (int)((tile / p.tiles_x) % p.tiles_y);
+                const long long nz = tile / tiles_per_plane;
+                const int z = p.z0 + (int)(nz % p.ZW), n = (int)(nz / p.ZW);
+                const int x0 = tx_i * TX, y0 = ty_i * TR;
+                for (int g = 0; g < ngroups; ++g, ++it) {
+                    if (it >= (uint32_t)S) split_wait(&empty[s], ph ^ 1u, abort_flag, p.status, 1);
+                    tma::mbar_arrive_expect_tx(&full[s], (uint32_t)(STAGE * 4));
+                    float *stage = ring + s * STAGE;
+                    // channels past C are outside the tensor maps: zero-filled, no traffic
+                    tma::tensor_g2s_5d(stage, &map_in, x0, y0, z, g * CB, n, &full[s]);
+                    tma::tensor_g2s_5d(stage + CB * CHAN, &map_gin, x0, y0, z, g * CB, n, &full[s]);
+                    if (g == halo_at && tile + gridDim.x < p.num_tiles) {
+                        split_wait(halo_empty, tcount & 1u, abort_flag, p.status, 5);
+                        issue_halo(tile + gridDim.x);
+                    }
+                    if (++s == (uint32_t)S) s = 0, ph ^= 1u;
+                }
+            }
+        }
+        return;
+    }
+
+    uint32_t tcount = 0, s = 0, ph = 0;
+    if (warp >= kSplitXWarps) {
+        // ===================================== K warps =====================================
+        // lane = tap (tz, ty, tx); Mk[v] = M_tap at voxel (row r, column x0 + KH * h + v)
+        // lane = (qw, tl): taps 4 tl + {0..3}; voxels 4 (4 j + qw) + {0..3}, j = 0..3, of the half row,
+        // so that the four quarter-warps read four neighbouring 16-byte pieces per load
+        const int kw = warp - kSplitXWarps, r = kw >> 1, h = kw & 1;
+        const int qw = lane >> 3, tl = lane & 7;
+        const bool hi = (lane & 16) != 0, mid = (lane & 8) != 0;
+        const int tfinal = 4 * tl + (hi ? 2 : 0) + (mid ? 1 : 0);  // the tap whose sum this lane ends up with
+        float *wslot = wacc + (size_t)kw * p.C * kSplitWaccPad + tfinal;
+        for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++tcount) {
+            const int tx_i = (int)(tile % p.tiles_x);
+            const int ty_i = (int)((tile / p.tiles_x) % p.tiles_y);
+            const long long nz = tile / tiles_per_plane;
+            const int z = p.z0 + (int)(nz % p.ZW), n = (int)(nz / p.ZW);
+            const int x0 = tx_i * TX, y0 = ty_i * TR;
+            split_wait(halo_full, tcount & 1u, abort_flag, p.status, 6);
+            split_fill_rows(p, rows, orows, HSLOT, TXP, gate, tid, n, z, y0, x0);
+            if (tcount) split_wait(m_done, (tcount - 1) & 1u, abort_flag, p.status, 7);
+            tma::named_barrier(1, kSplitConsumers);
+            split_build_table(p, rows, msm, HSLOT, TXP, TS, tid, x0);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tma::named_barrier(2, kSplitConsumers);
+
+            float2 Mk[4][KH / 8];  // [tap of the lane][pair of neighbouring voxels]: operands of packed FMAs
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const int ta = 4 * tl + a;
+                const float4 *m4 = reinterpret_cast<const float4 *>(msm + (ta < TAPS ? ta : 0) * TS + r * TX + KH * h);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float4 q = m4[4 * j + qw];
+                    if (ta >= TAPS) q = make_float4(0.f, 0.f, 0.f, 0.f);
+                    Mk[a][2 * j] = make_float2(q.x, q.y), Mk[a][2 * j + 1] = make_float2(q.z, q.w);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) tma::mbar_arrive(m_done);
+
+            for (int g = 0; g < ngroups; ++g) {
+#ifdef MSD_BWD_TIMING
+                const long long w0 = clock64();
+#endif
+                split_wait(&full[s], ph, abort_flag, p.status, 2);
+#ifdef MSD_BWD_TIMING
+                if (blockIdx.x == 0 && tid == 128 && p.timing) p.timing[7] += (unsigned long long)(clock64() - w0);  // K warp 0: waiting for a stage
+#endif
+                const float4 *ain0 = reinterpret_cast<const float4 *>(ring + s * STAGE + r * TX + KH * h) + qw;  // in[g * CB], this half row
+                float tot[CB];
+#pragma unroll
+                for (int cc = 0; cc < CB; ++cc) {
+                    const float4 *ain = ain0 + cc * (CHAN / 4);
+                    float4 av[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) av[j] = ain[4 * j];  // one 64-byte run per warp and load
+                    float2 acc[4];
+#pragma unroll
+                    for (int a = 0; a < 4; ++a) acc[a] = make_float2(0.f, 0.f);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+#pragma unroll
+                        for (int a = 0; a < 4; ++a) {
+                            acc[a] = __ffma2_rn(make_float2(av[j].x, av[j].y), Mk[a][2 * j], acc[a]);
+                            acc[a] = __ffma2_rn(make_float2(av[j].z, av[j].w), Mk[a][2 * j + 1], acc[a]);
+                        }
+                    // sums over the lane's 16 voxels, then a reduce-scatter over the four quarter-warps
+                    // (fixed tree): the lane keeps tap 4 tl + 2 hi + mid
+                    const float s0 = acc[0].x + acc[0].y, s1 = acc[1].x + acc[1].y, s2 = acc[2].x + acc[2].y, s3 = acc[3].x + acc[3].y;
+                    float k0 = hi ? s2 : s0, k1 = hi ? s3 : s1;
+                    k0 += __shfl_xor_sync(0xffffffffu, hi ? s0 : s2, 16);
+                    k1 += __shfl_xor_sync(0xffffffffu, hi ? s1 : s3, 16);
+                    float keep = mid ? k1 : k0;
+                    keep += __shfl_xor_sync(0xffffffffu, mid ? k0 : k1, 8);
+                    tot[cc] = keep;  // channels past C: zero-filled stage, sum 0
+                }
+                __syncwarp();
+                if (lane == 0) tma::mbar_arrive(&empty[s]);
+                if (tfinal < TAPS) {
+#pragma unroll
+                    for (int cc = 0; cc < CB; ++cc)
+                        if (g * CB + cc < p.C) wslot[(g * CB + cc) * kSplitWaccPad] += tot[cc];
+                }
+                if (++s == (uint32_t)S) s = 0, ph ^= 1u;
+            }
+        }
+    } else {
+        // ===================================== X warps =====================================
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSplitRegsX));
+        const int r = warp, xq = lane;
+        float bsum = 0.f;
+        for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++tcount) {
+            const int tx_i = (int)(tile % p.tiles_x);
+            const int ty_i = (int)((tile / p.tiles_x) % p.tiles_y);
+            const long long nz = tile / tiles_per_plane;
+            const int z = p.z0 + (int)(nz % p.ZW), n = (int)(nz / p.ZW);
+            const int x0 = tx_i * TX, y0 = ty_i * TR;
+            MSD_T(t0);
+            split_wait(halo_full, tcount & 1u, abort_flag, p.status, 6);
+            MSD_T(t1);
+            split_fill_rows(p, rows, orows, HSLOT, TXP, gate, tid, n, z, y0, x0);
+            if (tcount) split_wait(m_done, (tcount - 1) & 1u, abort_flag, p.status, 7);
+            tma::named_barrier(1, kSplitConsumers);
+            MSD_T(t2);
+            split_build_table(p, rows, msm, HSLOT, TXP, TS, tid, x0);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tma::named_barrier(2, kSplitConsumers);
+            if (tid == 0) tma::mbar_arrive(halo_empty);  // the TMA slots may take the next tile's rows
+            MSD_T(t3);
+
+            float2 M[TAPS][2];  // pairs of neighbouring voxels: operands of packed FMAs
+            const bool valid = (y0 + r) < p.Y;
+#pragma unroll
+            for (int t = 0; t < TAPS; ++t) {
+                const float4 q = *reinterpret_cast<const float4 *>(msm + t * TS + r * TX + 4 * xq);
+                M[t][0] = make_float2(q.x, q.y), M[t][1] = make_float2(q.z, q.w);
+            }
+            if (valid) bsum += (M[13][0].x + M[13][0].y) + (M[13][1].x + M[13][1].y);  // centre tap = m itself
+            __syncwarp();
+            if (lane == 0) tma::mbar_arrive(m_done);
+
+            float *gi_row = p.gin + n * p.gi_sn + z * p.gi_sz + (int64_t)(y0 + r) * p.gi_sy + x0 + 4 * xq;
+            MSD_T(t4);
+            for (int g = 0; g < ngroups; ++g) {
+                MSD_T(w0);
+                split_wait(&full[s], ph, abort_flag, p.status, 2);
+                MSD_T(w1);
+                MSD_TADD(6, w0, w1);  // X warp 0: waiting for a stage
+                const float *stage = ring + s * STAGE + r * TX + 4 * xq;
+                const bool live = valid && !*abort_flag;
+#pragma unroll
+                for (int cc = 0; cc < CB; ++cc) {
+                    const int c = g * CB + cc;
+                    if (c < p.C) {
+                        const float4 gq = ld4(stage + (CB + cc) * CHAN);
+                        float w[kSplitWPad];
+                        const float4 *wp = reinterpret_cast<const float4 *>(wsm + c * kSplitWPad);
+#pragma unroll
+                        for (int i = 0; i < kSplitWPad / 4; ++i) {
+                            const float4 t4 = wp[i];
+                            w[4 * i + 0] = t4.x, w[4 * i + 1] = t4.y, w[4 * i + 2] = t4.z, w[4 * i + 3] = t4.w;
+                        }
+                        float gv[4] = {gq.x, gq.y, gq.z, gq.w};
+#pragma unroll
+                        for (int t = 0; t < TAPS; ++t) {
+                            gv[0] = fmaf(w[t], M[t][0].x, gv[0]);
+                            gv[1] = fmaf(w[t], M[t][0].y, gv[1]);
+                            gv[2] = fmaf(w[t], M[t][1].x, gv[2]);
+                            gv[3] = fmaf(w[t], M[t][1].y, gv[3]);
+                        }
+                        if (c == p.mask_channel) {
+                            // this channel is the output of the layer below: hand its gradient
+                            // over already multiplied by that layer's ReLU gate
+                            const float4 a = ld4(stage + cc * CHAN);
+                            gv[0] = a.x > 0.f ? gv[0] : 0.f;
+                            gv[1] = a.y > 0.f ? gv[1] : 0.f;
+                            gv[2] = a.z > 0.f ? gv[2] : 0.f;
+                            gv[3] = a.w > 0.f ? gv[3] : 0.f;
+                        }
+                        if (live) *reinterpret_cast<float4 *>(gi_row + c * p.gi_sc) = make_float4(gv[0], gv[1], gv[2], gv[3]);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) tma::mbar_arrive(&empty[s]);
+                if (++s == (uint32_t)S) s = 0, ph ^= 1u;
+            }
+            MSD_T(t5);
+            MSD_TADD(0, t0, t1);  // wait for the halo rows
+            MSD_TADD(1, t1, t2);  // pass A + barrier
+            MSD_TADD(2, t2, t3);  // pass B + barrier
+            MSD_TADD(3, t3, t4);  // M registers
+            MSD_TADD(4, t4, t5);  // channel loop
+            MSD_TADD(5, 0, 1);    // tiles
+        }
+        if (p.part_b) {
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) bsum += __shfl_down_sync(0xffffffffu, bsum, off);
+            if (lane == 0) red[r] = bsum;
+        }
+    }
+
+    // ---- block epilogue: fixed-order sums of the K warps' slots, one partial per block ----
+    tma::named_barrier(1, kSplitConsumers);
+    if (!*abort_flag) {
+        float *dst = p.part_k + (int64_t)blockIdx.x * p.C * TAPS;
+        for (int i = tid; i < p.C * TAPS; i += kSplitConsumers) {
+            const int c = i / TAPS, t = i - c * TAPS;
+            float s_ = 0.f;
+#pragma unroll
+            for (int w = 0; w < kSplitKWarps; ++w) s_ += wacc[((size_t)w * p.C + c) * kSplitWaccPad + t];
+            dst[i] = s_;
+        }
+        if (p.part_b && tid == 0) {
+            float s_ = 0.f;
+#pragma unroll
+            for (int w = 0; w < kSplitXWarps; ++w) s_ += red[w];
+            p.part_b[blockIdx.x] = s_;
+        }
+    }
+}
+
+}  // namespace fast
+}  // namespace msd

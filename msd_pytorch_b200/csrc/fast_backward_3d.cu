@@ -1,5 +1,5 @@
 // 3D instantiations of the fused backward kernel (see fast_backward.cuh).
-#include "fast_backward.cuh"
+#include "fast_backward3d_split.cuh"
 
 namespace msd {
 namespace fast {
@@ -17,6 +17,14 @@ BwdLaunchFn bwd3d_launchers[2][3] = {
     {launch3d<32, 1, true, false>, launch3d<32, 1, false, true>, launch3d<32, 1, true, true>},
     {launch3d<16, 1, true, false>, launch3d<16, 1, false, true>, launch3d<16, 1, true, true>},
 };
+
+static int launch3d_split(const CUtensorMap *m, const BwdParams &p, int grid, size_t smem, cudaStream_t s) {
+    auto kern = fused_backward3d_split_kernel;
+    MSD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    MSD_CUDA_TRY(tma::launch_pdl(kern, dim3(grid), dim3(kSplitThreads), smem, s, m[0], m[1], m[2], m[3], p));
+    return MSD_OK;
+}
+BwdLaunchFn bwd3d_split_launcher = launch3d_split;
 
 }  // namespace fast
 }  // namespace msd

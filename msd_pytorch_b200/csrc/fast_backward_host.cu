@@ -11,6 +11,7 @@ namespace fast {
 int get_tensor_map(int device, const void *ptr, int rank, const int64_t *dims, const int64_t *strides, const int *box, CUtensorMap *out);
 extern BwdLaunchFn bwd2d_launchers[2][2][3];
 extern BwdLaunchFn bwd3d_launchers[2][3];
+extern BwdLaunchFn bwd3d_split_launcher;
 
 #ifdef MSD_BWD_TIMING
 static unsigned long long *g_dbg_timing = nullptr;
@@ -49,7 +50,13 @@ static bool aligned_view(const View *v) {
 struct BwdPlan {
     int txq16, j, stages, blocks_per_sm;
     size_t smem;
+    bool split;  // 3D kernel with X warps and K warps (fast_backward3d_split.cuh)
 };
+
+// geometry of the role-split 3D kernel (the constants of the same names there)
+static const int kSplitRows = 4, kSplitKWarps = 8, kSplitCB = 4, kSplitMaxDilation = 12, kSplitMaxStages = 8, kSplitHeader = 512;
+// below this many input channels the per-tile set-up of the split kernel outweighs its faster channel loop
+static const int kSplitMinChannels = 12;
 
 static bool plan(const BackwardArgs &a, BwdPlan *pl) {
     const View &g = *a.gout;
@@ -59,7 +66,22 @@ static bool plan(const BackwardArgs &a, BwdPlan *pl) {
     const bool do_x = a.gin != nullptr, do_k = a.gk != nullptr;
     const int Dp = (a.d + 3) & ~3;
     pl->txq16 = g.x <= 64 ? 1 : 0;
+    pl->split = false;
     const int TX = pl->txq16 ? 64 : 128;
+    if (nd == 3 && do_x && do_k && (g.x % 128) == 0 && a.d <= kSplitMaxDilation && C >= kSplitMinChannels && tuning_get(BWD3D, a.d) != 0) {
+        // role-split kernel: 4 X warps + 8 K warps on tiles of 4 rows x 128 columns, kSplitCB
+        // channels per ring stage; the table of M (27 taps x (4 x 128 + 4) floats) beside the halo rows
+        const int TR = kSplitRows, TXP = 128 + 2 * Dp;
+        const size_t halo = (size_t)RT * ((TR * TXP + 31) & ~31) * (a.out ? 2 : 1) + ((27 * (TR * 128 + 4) + 31) & ~31);
+        const size_t fixed = kSplitHeader + (size_t)4 * (C * TAPS_PAD + (size_t)kSplitKWarps * C * 28 + halo);
+        const size_t stage = (size_t)4 * 2 * kSplitCB * TR * 128;
+        if (fixed + 2 * stage <= kSmemBudget) {
+            int s = (int)((kSmemBudget - fixed) / stage);
+            if (s > kSplitMaxStages) s = kSplitMaxStages;
+            pl->j = 1, pl->stages = s, pl->blocks_per_sm = 1, pl->smem = fixed + (size_t)s * stage, pl->split = true;
+            return true;
+        }
+    }
     int j = 1;
     if (nd == 2) {
         const int tuned = tuning_get(BWD2D, a.d);
@@ -230,7 +252,7 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
     p.N = (int)g.n, p.C = (int)C, p.Z = (int)g.z, p.Y = (int)g.y, p.X = (int)g.x;
     p.d = a.d, p.Dp = (a.d + 3) & ~3;
     const int TX = pl.txq16 ? 64 : 128;
-    const int TR = (bwd_consumer_warps(a.nd) * 32 / (TX / 4)) * pl.j;
+    const int TR = pl.split ? kSplitRows : (bwd_consumer_warps(a.nd) * 32 / (TX / 4)) * pl.j;
     get_z_window((int)g.z, &p.z0, &p.ZW);
     p.tiles_x = (int)ceil_div(g.x, TX);
     p.tiles_y = (int)ceil_div(g.y, TR);
@@ -272,7 +294,7 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
         const View *views[4] = {do_k ? a.in : a.gin, do_x ? a.gin : a.in, a.gout, a.out ? a.out : a.gout};
         for (int which = 0; which < 4; ++which) {
             const View *v = views[which];
-            int box[5] = {which < 2 ? TX : TX + 2 * p.Dp, TR, 1, 1, 1};
+            int box[5] = {which < 2 ? TX : TX + 2 * p.Dp, TR, 1, (pl.split && which < 2) ? kSplitCB : 1, 1};
             int64_t dims[5], strides[5];
             if (a.nd == 3) {
                 dims[0] = v->x, dims[1] = v->y, dims[2] = v->z, dims[3] = v->c, dims[4] = v->n;
@@ -286,7 +308,7 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
         }
     }
     const int mode = do_x && do_k ? 2 : (do_k ? 1 : 0);
-    BwdLaunchFn fn = a.nd == 3 ? bwd3d_launchers[pl.txq16][mode] : bwd2d_launchers[pl.txq16][pl.j - 1][mode];
+    BwdLaunchFn fn = a.nd == 3 ? (pl.split ? bwd3d_split_launcher : bwd3d_launchers[pl.txq16][mode]) : bwd2d_launchers[pl.txq16][pl.j - 1][mode];
     int rc = fn(maps, p, grid, pl.smem, s);
     if (rc) return rc;
     count_launch(true);

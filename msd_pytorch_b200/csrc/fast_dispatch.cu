@@ -15,6 +15,7 @@ int num_variants(int family) {
         case FWD2D: return num_forward2d_variants();  // lattice rows x column segments x tile width
         case BWD2D: return 2;  // 4 / 8 voxels per thread
         case FWD3D: return 2;  // 4 / 2 column segments per thread
+        case BWD3D: return 2;  // unsplit consumers / X warps + K warps
         default: return 1;
     }
 }

@@ -182,3 +182,54 @@ def test_forward3d_launch_variants(cc, cuda_device, d, variant):
         assert_close(y, y_o, 1e-4, "forward3d variant %d" % variant)
     finally:
         _lib.lib.msd_tuning_set(_lib.FAMILY_FWD3D, d, -1)
+
+
+@pytest.mark.parametrize("sp,B,depth", [((13, 23, 256), 2, 22), ((10, 11, 128), 1, 30), ((24, 40, 384), 1, 15)])
+def test_backward3d_role_split_variant(cuda_device, sp, B, depth):
+    """The role-split 3D backward (variant 1: X warps + K warps; layers of 12 and more input
+    channels) == the three single ops per layer, which the tests above hold against the oracle:
+    ragged tiles in y, one and several tiles in x (both x borders in one tile when X == 128),
+    every dilation 1..10, channel counts that are and are not multiples of the stage's 4."""
+    from msd_pytorch_b200 import _lib
+    from msd_pytorch_b200 import msd_custom_convolutions as cc
+    from msd_pytorch_b200.msd_block import block_backward_, block_forward_
+
+    dev = cuda_device
+    assert _lib.lib.msd_tuning_num_variants(_lib.FAMILY_BWD3D) == 2
+    torch.manual_seed(17)
+    dil = [1 + (i % 10) for i in range(depth)]
+    ws = [torch.randn(1, 1 + i, 3, 3, 3, device=dev) * (2.0 / (27 * (1 + i))) ** 0.5 for i in range(depth)]
+    bias = 0.05 * torch.randn(depth, device=dev)
+    res = torch.empty(B, 1 + depth, *sp, device=dev)
+    res[:, :1] = torch.randn(B, 1, *sp, device=dev)
+    block_forward_(res, 1, dil, bias, ws)
+    gout = torch.randn_like(res)
+    g2 = gout.clone()
+    gw2 = [torch.zeros_like(w) for w in ws]
+    gb2 = torch.zeros_like(bias)
+    for i in range(depth - 1, -1, -1):
+        n = 1 + i
+        cc.conv_relu_backward_x(res[:, n:n + 1], g2[:, n:n + 1], ws[i], g2[:, :n], dil[i])
+        cc.conv_relu_backward_k(res[:, n:n + 1], g2[:, n:n + 1], res[:, :n], gw2[i], dil[i])
+        cc.conv_relu_backward_bias(res[:, n:n + 1], g2[:, n:n + 1], gb2[i:i + 1])
+    for d in range(1, 11):
+        _lib.check(_lib.lib.msd_tuning_set(_lib.FAMILY_BWD3D, d, 1))
+    try:
+        g1 = gout.clone()
+        gw1 = [torch.zeros_like(w) for w in ws]
+        gb1 = torch.zeros_like(bias)
+        block_backward_(res, g1, 1, dil, ws, gw1, gb1)
+        assert _status(dev) == 0
+        assert_close(g1[:, :1], g2[:, :1], 1e-5, "grad_input")
+        assert_close(gb1, gb2, 1e-5, "grad_bias")
+        for i, (a, b) in enumerate(zip(gw1, gw2)):
+            assert_close(a, b, 1e-5, "grad_weight of layer %d" % i)
+        g3 = gout.clone()
+        gw3 = [torch.zeros_like(w) for w in ws]
+        gb3 = torch.zeros_like(bias)
+        block_backward_(res, g3, 1, dil, ws, gw3, gb3)
+        torch.cuda.synchronize()
+        assert torch.equal(g1[:, :1], g3[:, :1]) and torch.equal(gb1, gb3) and all(torch.equal(a, b) for a, b in zip(gw1, gw3))
+    finally:
+        for d in range(1, 11):
+            _lib.lib.msd_tuning_set(_lib.FAMILY_BWD3D, d, -1)

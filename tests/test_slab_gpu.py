@@ -9,16 +9,18 @@ from util import assert_close
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("X,depth", [(136, 7), (128, 15)])
 @pytest.mark.parametrize("world", [2, 3])
-def test_virtual_slabs_match_single_device(cuda_device, world):
+def test_virtual_slabs_match_single_device(cuda_device, world, X, depth):
+    # X = 128 with 12 and more input channels runs the role-split 3D backward in slab mode
     from msd_pytorch_b200 import _lib
     from msd_pytorch_b200.distributed import SlabBlock, SlabPlan, VirtualRanks, slab_backward, slab_forward
     from msd_pytorch_b200.msd_block import block_backward_, block_forward_
 
     dev = cuda_device
     torch.manual_seed(21)
-    Z, Y, X, depth = 36, 24, 136, 7
-    dil = [1, 2, 3, 4, 5, 6, 10]
+    Z, Y = 36, 24
+    dil = [1, 2, 3, 4, 5, 6, 10] if depth == 7 else [1 + (i % 10) for i in range(depth)]
     halo = 10
     ws = [torch.randn(1, 1 + i, 3, 3, 3, device=dev) * (2.0 / (27 * (1 + i))) ** 0.5 for i in range(depth)]
     bias = 0.05 * torch.randn(depth, device=dev)
