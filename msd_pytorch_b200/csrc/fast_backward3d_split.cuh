@@ -49,7 +49,7 @@ constexpr int kSplitWPad = 28;                                    // floats per 
 constexpr int kSplitMaxD = 12;                                    // border columns handled per side
 constexpr int kSplitMaxStages = 8;
 constexpr int kSplitHeaderBytes = 512;                            // barriers, abort flag, bias slots
-constexpr int kSplitRegsX = 176, kSplitRegsP = 24;
+constexpr int kSplitRegsX = 216, kSplitRegsP = 24;  // 128 x 216 + 256 x 128 + 128 x 24 <= 65536 registers
 
 // Bounded wait with a fast path: one try_wait before the generic bounded loop.
 __device__ __forceinline__ void split_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
@@ -109,37 +109,27 @@ __device__ __forceinline__ void split_fill_rows(const BwdParams &p, float *rows,
 
 // Pass B: the table  msm[t * TS + row * 128 + i] = M_t at voxel (row, x0 + i),  t = (tz, ty, tx):
 // the row of m that tap (tz, ty) reads, shifted by -d (tx - 1) columns, plus the mirrored x
-// source next to the left (tx = 0) / right (tx = 2) border of the image.
+// source next to the left (tx = 0) / right (tx = 2) border of the image.  One (tap, row) per
+// warp and step, lanes on consecutive floats: every load and store is conflict-free whatever
+// the shift.
 __device__ __forceinline__ void split_build_table(const BwdParams &p, const float *rows, float *msm, int HSLOT, int TXP, int TS, int ctid, int x0) {
     constexpr int TAPS = 27, TR = kSplitRows, TX = kSplitTX;
     const bool fold_l = x0 == 0, fold_r = x0 + TX == p.X;
+    const int lane = ctid & 31;
 #pragma unroll 3
-    for (int item = ctid; item < TAPS * TR * (TX / 4); item += kSplitConsumers) {
-        const int xq = item & 31, rr = (item >> 5) & 3, t = item >> 7;
+    for (int item = ctid >> 5; item < TAPS * TR; item += kSplitConsumerWarps) {
+        const int t = item / TR, rr = item - t * TR;
         const int rt = t / 3, tx = t - 3 * rt;
         const float *row = rows + rt * HSLOT + rr * TXP + p.Dp;  // row[i] <-> image x = x0 + i
-        const int i0 = 4 * xq;
-        float4 v;
-        if (tx == 1) {
-            v = *reinterpret_cast<const float4 *>(row + i0);
-        } else {
-            const float *src = row + i0 - p.d * (tx - 1);
-            v = make_float4(src[0], src[1], src[2], src[3]);
-            if (tx == 0 && fold_l && i0 < p.d) {  // columns q <= d - 1 also get the source d - 1 - q
-                v.x += row[p.d - 1 - i0];
-                if (i0 + 1 < p.d) v.y += row[p.d - 2 - i0];
-                if (i0 + 2 < p.d) v.z += row[p.d - 3 - i0];
-                if (i0 + 3 < p.d) v.w += row[p.d - 4 - i0];
-            }
-            if (tx == 2 && fold_r && i0 + 3 >= TX - p.d) {  // columns q >= X - d also get 2X - 1 - q - d
-                const int b = 2 * TX - 1 - p.d - i0;         // local source column of element 0
-                if (i0 + 0 >= TX - p.d) v.x += row[b];
-                if (i0 + 1 >= TX - p.d) v.y += row[b - 1];
-                if (i0 + 2 >= TX - p.d) v.z += row[b - 2];
-                v.w += row[b - 3];
-            }
-        }
-        *reinterpret_cast<float4 *>(msm + t * TS + rr * TX + i0) = v;
+        const float *src = row - p.d * (tx - 1) + lane;
+        float v[TX / 32];
+#pragma unroll
+        for (int k = 0; k < TX / 32; ++k) v[k] = src[32 * k];
+        if (tx == 0 && fold_l && lane < p.d) v[0] += row[p.d - 1 - lane];                  // columns q <= d - 1 also get the source d - 1 - q
+        if (tx == 2 && fold_r && lane >= 32 - p.d) v[TX / 32 - 1] += row[TX + 31 - p.d - lane];  // columns q >= X - d also get 2X - 1 - q - d
+        float *dst = msm + t * TS + rr * TX + lane;
+#pragma unroll
+        for (int k = 0; k < TX / 32; ++k) dst[32 * k] = v[k];
     }
 }
 
@@ -296,31 +286,44 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
 #endif
                 const float4 *ain0 = reinterpret_cast<const float4 *>(ring + s * STAGE + r * TX + KH * h) + qw;  // in[g * CB], this half row
                 float tot[CB];
+                // two channels at a time: eight independent chains of packed FMAs, and one
+                // reduce-scatter over the four quarter-warps (fixed tree) for both of them, so
+                // that its two shuffle rounds are paid once per pair.  Channels past C read a
+                // zero-filled stage.
 #pragma unroll
-                for (int cc = 0; cc < CB; ++cc) {
-                    const float4 *ain = ain0 + cc * (CHAN / 4);
-                    float4 av[4];
+                for (int cp = 0; cp < CB; cp += 2) {
+                    const float4 *ain = ain0 + cp * (CHAN / 4);
+                    float4 av[2][4];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) av[j] = ain[4 * j];  // one 64-byte run per warp and load
-                    float2 acc[4];
+                    for (int u = 0; u < 2; ++u)
 #pragma unroll
-                    for (int a = 0; a < 4; ++a) acc[a] = make_float2(0.f, 0.f);
+                        for (int j = 0; j < 4; ++j) av[u][j] = ain[u * (CHAN / 4) + 4 * j];  // one 64-byte run per warp and load
+                    float2 acc[2][4];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u)
+#pragma unroll
+                        for (int a = 0; a < 4; ++a) acc[u][a] = make_float2(0.f, 0.f);
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
 #pragma unroll
-                        for (int a = 0; a < 4; ++a) {
-                            acc[a] = __ffma2_rn(make_float2(av[j].x, av[j].y), Mk[a][2 * j], acc[a]);
-                            acc[a] = __ffma2_rn(make_float2(av[j].z, av[j].w), Mk[a][2 * j + 1], acc[a]);
-                        }
-                    // sums over the lane's 16 voxels, then a reduce-scatter over the four quarter-warps
-                    // (fixed tree): the lane keeps tap 4 tl + 2 hi + mid
-                    const float s0 = acc[0].x + acc[0].y, s1 = acc[1].x + acc[1].y, s2 = acc[2].x + acc[2].y, s3 = acc[3].x + acc[3].y;
-                    float k0 = hi ? s2 : s0, k1 = hi ? s3 : s1;
-                    k0 += __shfl_xor_sync(0xffffffffu, hi ? s0 : s2, 16);
-                    k1 += __shfl_xor_sync(0xffffffffu, hi ? s1 : s3, 16);
-                    float keep = mid ? k1 : k0;
-                    keep += __shfl_xor_sync(0xffffffffu, mid ? k0 : k1, 8);
-                    tot[cc] = keep;  // channels past C: zero-filled stage, sum 0
+                        for (int a = 0; a < 4; ++a)
+#pragma unroll
+                            for (int u = 0; u < 2; ++u) {
+                                acc[u][a] = __ffma2_rn(make_float2(av[u][j].x, av[u][j].y), Mk[a][2 * j], acc[u][a]);
+                                acc[u][a] = __ffma2_rn(make_float2(av[u][j].z, av[u][j].w), Mk[a][2 * j + 1], acc[u][a]);
+                            }
+                    float k0[2], k1[2];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        // sums over the lane's 16 voxels; the lane keeps taps {2 hi, 2 hi + 1} of its four
+                        const float s0 = acc[u][0].x + acc[u][0].y, s1 = acc[u][1].x + acc[u][1].y;
+                        const float s2 = acc[u][2].x + acc[u][2].y, s3 = acc[u][3].x + acc[u][3].y;
+                        k0[u] = (hi ? s2 : s0) + __shfl_xor_sync(0xffffffffu, hi ? s0 : s2, 16);
+                        k1[u] = (hi ? s3 : s1) + __shfl_xor_sync(0xffffffffu, hi ? s1 : s3, 16);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 2; ++u)  // ... then tap 2 hi + mid
+                        tot[cp + u] = (mid ? k1[u] : k0[u]) + __shfl_xor_sync(0xffffffffu, mid ? k0[u] : k1[u], 8);
                 }
                 __syncwarp();
                 if (lane == 0) tma::mbar_arrive(&empty[s]);
@@ -376,36 +379,53 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
                 MSD_TADD(6, w0, w1);  // X warp 0: waiting for a stage
                 const float *stage = ring + s * STAGE + r * TX + 4 * xq;
                 const bool live = valid && !*abort_flag;
+                // two channels at a time: eight independent FMA chains that share the M operands.
+                // When C is odd the last pair's second channel reads a zero-filled stage and
+                // whatever follows the weights in shared memory; its result is not stored.
 #pragma unroll
-                for (int cc = 0; cc < CB; ++cc) {
-                    const int c = g * CB + cc;
+                for (int cp = 0; cp < CB; cp += 2) {
+                    const int c = g * CB + cp;
                     if (c < p.C) {
-                        const float4 gq = ld4(stage + (CB + cc) * CHAN);
-                        float w[kSplitWPad];
-                        const float4 *wp = reinterpret_cast<const float4 *>(wsm + c * kSplitWPad);
+                        const float4 gq0 = ld4(stage + (CB + cp) * CHAN), gq1 = ld4(stage + (CB + cp + 1) * CHAN);
+                        const float4 *wp0 = reinterpret_cast<const float4 *>(wsm + c * kSplitWPad);
+                        const float4 *wp1 = wp0 + kSplitWPad / 4;
+                        float gv0[4] = {gq0.x, gq0.y, gq0.z, gq0.w}, gv1[4] = {gq1.x, gq1.y, gq1.z, gq1.w};
+                        float4 wa = wp0[0], wb = wp1[0];
 #pragma unroll
                         for (int i = 0; i < kSplitWPad / 4; ++i) {
-                            const float4 t4 = wp[i];
-                            w[4 * i + 0] = t4.x, w[4 * i + 1] = t4.y, w[4 * i + 2] = t4.z, w[4 * i + 3] = t4.w;
-                        }
-                        float gv[4] = {gq.x, gq.y, gq.z, gq.w};
+                            const float w0[4] = {wa.x, wa.y, wa.z, wa.w}, w1[4] = {wb.x, wb.y, wb.z, wb.w};
+                            if (i + 1 < kSplitWPad / 4) wa = wp0[i + 1], wb = wp1[i + 1];  // the next four taps, ahead of this quad's FMAs
 #pragma unroll
-                        for (int t = 0; t < TAPS; ++t) {
-                            gv[0] = fmaf(w[t], M[t][0].x, gv[0]);
-                            gv[1] = fmaf(w[t], M[t][0].y, gv[1]);
-                            gv[2] = fmaf(w[t], M[t][1].x, gv[2]);
-                            gv[3] = fmaf(w[t], M[t][1].y, gv[3]);
+                            for (int q = 0; q < 4; ++q) {
+                                const int t = 4 * i + q;
+                                if (t < TAPS) {
+                                    gv0[0] = fmaf(w0[q], M[t][0].x, gv0[0]), gv1[0] = fmaf(w1[q], M[t][0].x, gv1[0]);
+                                    gv0[1] = fmaf(w0[q], M[t][0].y, gv0[1]), gv1[1] = fmaf(w1[q], M[t][0].y, gv1[1]);
+                                    gv0[2] = fmaf(w0[q], M[t][1].x, gv0[2]), gv1[2] = fmaf(w1[q], M[t][1].x, gv1[2]);
+                                    gv0[3] = fmaf(w0[q], M[t][1].y, gv0[3]), gv1[3] = fmaf(w1[q], M[t][1].y, gv1[3]);
+                                }
+                            }
                         }
+                        // a channel that is the output of the layer below: hand its gradient over
+                        // already multiplied by that layer's ReLU gate
                         if (c == p.mask_channel) {
-                            // this channel is the output of the layer below: hand its gradient
-                            // over already multiplied by that layer's ReLU gate
-                            const float4 a = ld4(stage + cc * CHAN);
-                            gv[0] = a.x > 0.f ? gv[0] : 0.f;
-                            gv[1] = a.y > 0.f ? gv[1] : 0.f;
-                            gv[2] = a.z > 0.f ? gv[2] : 0.f;
-                            gv[3] = a.w > 0.f ? gv[3] : 0.f;
+                            const float4 a = ld4(stage + cp * CHAN);
+                            gv0[0] = a.x > 0.f ? gv0[0] : 0.f;
+                            gv0[1] = a.y > 0.f ? gv0[1] : 0.f;
+                            gv0[2] = a.z > 0.f ? gv0[2] : 0.f;
+                            gv0[3] = a.w > 0.f ? gv0[3] : 0.f;
                         }
-                        if (live) *reinterpret_cast<float4 *>(gi_row + c * p.gi_sc) = make_float4(gv[0], gv[1], gv[2], gv[3]);
+                        if (c + 1 == p.mask_channel) {
+                            const float4 a = ld4(stage + (cp + 1) * CHAN);
+                            gv1[0] = a.x > 0.f ? gv1[0] : 0.f;
+                            gv1[1] = a.y > 0.f ? gv1[1] : 0.f;
+                            gv1[2] = a.z > 0.f ? gv1[2] : 0.f;
+                            gv1[3] = a.w > 0.f ? gv1[3] : 0.f;
+                        }
+                        if (live) {
+                            *reinterpret_cast<float4 *>(gi_row + c * p.gi_sc) = make_float4(gv0[0], gv0[1], gv0[2], gv0[3]);
+                            if (c + 1 < p.C) *reinterpret_cast<float4 *>(gi_row + (c + 1) * p.gi_sc) = make_float4(gv1[0], gv1[1], gv1[2], gv1[3]);
+                        }
                     }
                 }
                 __syncwarp();

@@ -56,7 +56,7 @@ struct BwdPlan {
 // geometry of the role-split 3D kernel (the constants of the same names there)
 static const int kSplitRows = 4, kSplitKWarps = 8, kSplitCB = 4, kSplitMaxDilation = 12, kSplitMaxStages = 8, kSplitHeader = 512;
 // below this many input channels the per-tile set-up of the split kernel outweighs its faster channel loop
-static const int kSplitMinChannels = 12;
+static const int kSplitMinChannels = 8;
 
 static bool plan(const BackwardArgs &a, BwdPlan *pl) {
     const View &g = *a.gout;
