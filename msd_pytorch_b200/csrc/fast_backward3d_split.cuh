@@ -240,12 +240,15 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
     if (warp >= kSplitXWarps) {
         // ===================================== K warps =====================================
         // lane = tap (tz, ty, tx); Mk[v] = M_tap at voxel (row r, column x0 + KH * h + v)
-        // lane = (qw, tl): taps 4 tl + {0..3}; voxels 4 (4 j + qw) + {0..3}, j = 0..3, of the half row,
-        // so that the four quarter-warps read four neighbouring 16-byte pieces per load
+        // lane = (qw, tl): taps tl + 8 {0..3}; voxels 4 (4 j + qw) + {0..3}, j = 0..3, of the half row.
+        // The four quarter-warps read four neighbouring 16-byte pieces of the activations per
+        // load; the eight lanes of a quarter-warp (one phase of a 128-bit shared load) read
+        // eight neighbouring taps of the table, whose tap stride of 4 mod 32 banks spreads them
+        // over all banks.
         const int kw = warp - kSplitXWarps, r = kw >> 1, h = kw & 1;
         const int qw = lane >> 3, tl = lane & 7;
         const bool hi = (lane & 16) != 0, mid = (lane & 8) != 0;
-        const int tfinal = 4 * tl + (hi ? 2 : 0) + (mid ? 1 : 0);  // the tap whose sum this lane ends up with
+        const int tfinal = tl + 8 * ((hi ? 2 : 0) + (mid ? 1 : 0));  // the tap whose sum this lane ends up with
         float *wslot = wacc + (size_t)kw * p.C * kSplitWaccPad + tfinal;
         for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++tcount) {
             const int tx_i = (int)(tile % p.tiles_x);
@@ -261,10 +264,13 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tma::named_barrier(2, kSplitConsumers);
 
+#ifdef MSD_BWD_TIMING
+            const long long k0t = clock64();
+#endif
             float2 Mk[4][KH / 8];  // [tap of the lane][pair of neighbouring voxels]: operands of packed FMAs
 #pragma unroll
             for (int a = 0; a < 4; ++a) {
-                const int ta = 4 * tl + a;
+                const int ta = tl + 8 * a;
                 const float4 *m4 = reinterpret_cast<const float4 *>(msm + (ta < TAPS ? ta : 0) * TS + r * TX + KH * h);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -275,6 +281,10 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
             }
             __syncwarp();
             if (lane == 0) tma::mbar_arrive(m_done);
+#ifdef MSD_BWD_TIMING
+            if (blockIdx.x == 0 && tid == 128 && p.timing) p.timing[11] += (unsigned long long)(clock64() - k0t);  // K warp 0: M registers
+            const long long k1t = clock64();
+#endif
 
             for (int g = 0; g < ngroups; ++g) {
 #ifdef MSD_BWD_TIMING
@@ -334,6 +344,9 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
                 }
                 if (++s == (uint32_t)S) s = 0, ph ^= 1u;
             }
+#ifdef MSD_BWD_TIMING
+            if (blockIdx.x == 0 && tid == 128 && p.timing) p.timing[12] += (unsigned long long)(clock64() - k1t);  // K warp 0: channel loop
+#endif
         }
     } else {
         // ===================================== X warps =====================================
@@ -350,14 +363,20 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
             split_wait(halo_full, tcount & 1u, abort_flag, p.status, 6);
             MSD_T(t1);
             split_fill_rows(p, rows, orows, HSLOT, TXP, gate, tid, n, z, y0, x0);
+            MSD_T(t1a);
             if (tcount) split_wait(m_done, (tcount - 1) & 1u, abort_flag, p.status, 7);
             tma::named_barrier(1, kSplitConsumers);
             MSD_T(t2);
             split_build_table(p, rows, msm, HSLOT, TXP, TS, tid, x0);
+            MSD_T(t2a);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            MSD_T(t2b);
+            MSD_TADD(10, t2a, t2b);  // the proxy fence
             tma::named_barrier(2, kSplitConsumers);
             if (tid == 0) tma::mbar_arrive(halo_empty);  // the TMA slots may take the next tile's rows
             MSD_T(t3);
+            MSD_TADD(8, t1, t1a);   // pass A alone
+            MSD_TADD(9, t2, t2a);   // pass B alone
 
             float2 M[TAPS][2];  // pairs of neighbouring voxels: operands of packed FMAs
             const bool valid = (y0 + r) < p.Y;

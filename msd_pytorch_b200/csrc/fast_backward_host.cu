@@ -18,8 +18,8 @@ static unsigned long long *g_dbg_timing = nullptr;
 extern "C" MSD_API void msd_debug_bwd_timing(unsigned long long *out) {
     cudaDeviceSynchronize();
     if (g_dbg_timing) {
-        cudaMemcpy(out, g_dbg_timing, 64, cudaMemcpyDeviceToHost);
-        cudaMemset(g_dbg_timing, 0, 64);
+        cudaMemcpy(out, g_dbg_timing, 128, cudaMemcpyDeviceToHost);
+        cudaMemset(g_dbg_timing, 0, 128);
     }
 }
 #endif
@@ -265,8 +265,8 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
     {
         static unsigned long long *dbg = nullptr;
         if (!dbg) {
-            cudaMalloc(&dbg, 64);
-            cudaMemset(dbg, 0, 64);
+            cudaMalloc(&dbg, 128);
+            cudaMemset(dbg, 0, 128);
         }
         p.timing = dbg;
         g_dbg_timing = dbg;
