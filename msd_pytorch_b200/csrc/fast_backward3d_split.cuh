@@ -14,19 +14,23 @@
 // A tile is 4 rows x 128 columns of one z-plane.  The block has four warpgroups:
 //   warps 0-3    X warps, one per tile row               (registers raised to kSplitRegsX)
 //   warps 4-11   K warps, (row, half) = (w-4)/2, (w-4)%2 (the launch's 128 registers)
-//   warp 12      TMA producer; warps 13-15 exit at once  (registers lowered to kSplitRegsP)
+//   warp 12      TMA producer                            (registers lowered to kSplitRegsP)
+//   warps 13-15  builders of the table of M (below)      (same warpgroup as the producer)
 // so that each of the four warp schedulers (warp id mod 4) carries one X warp and two K warps.
 // The register file is re-divided between the warpgroups with setmaxnreg: the X warps need
-// 108 registers for M alone, the producer next to none.
+// 108 registers for M alone, the producer and the builders few.
 //
 // Data movement.  One ring stage holds kSplitCB consecutive channels of the tile: two TMA
 // boxes (activations, gradients) of kSplitCB x 4 x 128 floats, so that the cost of issuing a
 // copy and of the full/empty hand-shake is paid once per kSplitCB channels.  The 9 halo row
-// groups of gout (and of out, for the ReLU gate) land by TMA.  The consumers turn them into
-// the table  Msm[t][row][x] = M_t(voxel)  in two short cooperative passes (gate + y/z folds in
-// place; x shifts + x folds into the table) and both kinds of warps then fill their registers
+// groups of gout (and of out, for the ReLU gate) land by TMA.  The builder warps turn them into
+// the table  Msm[t][row][x] = M_t(voxel)  in two short passes (gate + y/z folds in place; x
+// shifts + x folds into the table) while the consumers are still streaming the channels of
+// the previous tile; both kinds of consumer warps then fill their registers from the table
 // with aligned 128-bit loads and no arithmetic.  The table's tap stride is 4 mod 32 banks,
-// which makes the K warps' lane-per-tap loads conflict-free.
+// which makes the K warps' lane-per-tap loads conflict-free.  Hand-shakes: halo_full
+// (producer -> builders), halo_empty (builders -> producer), table_full (builders ->
+// consumers), m_done (consumers -> builders: the table may be overwritten).
 //
 // Requirements (checked by the host): X a multiple of 128, dilation <= 12, both gradients wanted.
 #pragma once
@@ -49,7 +53,9 @@ constexpr int kSplitWPad = 28;                                    // floats per 
 constexpr int kSplitMaxD = 12;                                    // border columns handled per side
 constexpr int kSplitMaxStages = 8;
 constexpr int kSplitHeaderBytes = 512;                            // barriers, abort flag, bias slots
-constexpr int kSplitRegsX = 216, kSplitRegsP = 24;  // 128 x 216 + 256 x 128 + 128 x 24 <= 65536 registers
+constexpr int kSplitBuilderWarps = 3;                             // warps 13-15
+constexpr int kSplitBuilders = kSplitBuilderWarps * 32;
+constexpr int kSplitRegsX = 192, kSplitRegsP = 64;  // 128 x 192 + 256 x 128 + 128 x 64 = 65536 registers
 
 // Bounded wait with a fast path: one try_wait before the generic bounded loop.
 __device__ __forceinline__ void split_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
@@ -59,9 +65,9 @@ __device__ __forceinline__ void split_wait(uint64_t *bar, uint32_t parity, volat
 
 // Pass A: turns the halo rows of one tile (landed by TMA in `rows` / `orows`, slots of HSLOT
 // floats) into the rows of m, in place: ReLU gate, plus the mirrored y / z sources next to
-// the volume's borders.  Cooperative over the kSplitConsumers consumer threads; the caller
-// synchronises them afterwards.
-__device__ __forceinline__ void split_fill_rows(const BwdParams &p, float *rows, const float *orows, int HSLOT, int TXP, bool gate, int ctid, int n,
+// the volume's borders.  Cooperative over the kSplitBuilders builder threads (index btid); the
+// caller synchronises them afterwards.
+__device__ __forceinline__ void split_fill_rows(const BwdParams &p, float *rows, const float *orows, int HSLOT, int TXP, bool gate, int btid, int n,
                                                 int z, int y0, int x0) {
     constexpr int RT = 9, TR = kSplitRows;
     const bool fold_rows = (y0 < p.d) || (y0 + TR + p.d > p.Y) || (z < p.d || z + p.d >= p.Z);
@@ -69,7 +75,8 @@ __device__ __forceinline__ void split_fill_rows(const BwdParams &p, float *rows,
     const float *go_n = p.gout + n * p.go_sn;
     const float *out_n = gate ? p.out + n * p.out_sn : nullptr;
     const int quads = TXP / 4;
-    for (int item = ctid; item < RT * TR * quads; item += kSplitConsumers) {
+#pragma unroll 1
+    for (int item = btid; item < RT * TR * quads; item += kSplitBuilders) {
         const int rowid = item / quads, q4 = item - rowid * quads;
         const int rt = rowid / TR, rr = rowid - rt * TR;
         const int soff = rt * HSLOT + rr * TXP + 4 * q4;
@@ -110,14 +117,14 @@ __device__ __forceinline__ void split_fill_rows(const BwdParams &p, float *rows,
 // Pass B: the table  msm[t * TS + row * 128 + i] = M_t at voxel (row, x0 + i),  t = (tz, ty, tx):
 // the row of m that tap (tz, ty) reads, shifted by -d (tx - 1) columns, plus the mirrored x
 // source next to the left (tx = 0) / right (tx = 2) border of the image.  One (tap, row) per
-// warp and step, lanes on consecutive floats: every load and store is conflict-free whatever
-// the shift.
-__device__ __forceinline__ void split_build_table(const BwdParams &p, const float *rows, float *msm, int HSLOT, int TXP, int TS, int ctid, int x0) {
+// builder warp and step, lanes on consecutive floats: every load and store is conflict-free
+// whatever the shift.
+__device__ __forceinline__ void split_build_table(const BwdParams &p, const float *rows, float *msm, int HSLOT, int TXP, int TS, int btid, int x0) {
     constexpr int TAPS = 27, TR = kSplitRows, TX = kSplitTX;
     const bool fold_l = x0 == 0, fold_r = x0 + TX == p.X;
-    const int lane = ctid & 31;
-#pragma unroll 3
-    for (int item = ctid >> 5; item < TAPS * TR; item += kSplitConsumerWarps) {
+    const int lane = btid & 31;
+#pragma unroll 4
+    for (int item = btid >> 5; item < TAPS * TR; item += kSplitBuilderWarps) {
         const int t = item / TR, rr = item - t * TR;
         const int rt = t / 3, tx = t - 3 * rt;
         const float *row = rows + rt * HSLOT + rr * TXP + p.Dp;  // row[i] <-> image x = x0 + i
@@ -147,7 +154,8 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
     uint64_t *halo_full = empty + kSplitMaxStages;  // the halo rows of a tile have landed
     uint64_t *halo_empty = halo_full + 1;           // ... have been turned into the table: the slots are free
     uint64_t *m_done = halo_empty + 1;              // every consumer warp has its M registers: the table is free
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(m_done + 1);
+    uint64_t *table_full = m_done + 1;              // the table of a tile is complete
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(table_full + 1);
     float *red = reinterpret_cast<float *>(smem_raw + 384);
     const int TXP = TX + 2 * p.Dp;
     const bool gate = p.out != nullptr;
@@ -172,6 +180,7 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
         tma::mbar_init(halo_full, 1);
         tma::mbar_init(halo_empty, 1);
         tma::mbar_init(m_done, kSplitConsumerWarps);
+        tma::mbar_init(table_full, 1);
         *abort_flag = 0;
         tma::fence_barrier_init();
     }
@@ -187,7 +196,7 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
     const long long tiles_per_plane = (long long)p.tiles_x * p.tiles_y;
 
     if (warp >= kSplitConsumerWarps) {
-        // ------------------- producer warpgroup: warp 12 issues, 13-15 leave -------------------
+        // ------------------- producer warpgroup: warp 12 issues the copies -------------------
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kSplitRegsP));
         if (warp == kSplitConsumerWarps && lane == 0) {
             tma::prefetch_tensormap(&map_in);
@@ -232,6 +241,29 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
                     if (++s == (uint32_t)S) s = 0, ph ^= 1u;
                 }
             }
+        } else if (warp > kSplitConsumerWarps) {
+            // ---------------- builder warps: the table of the NEXT tile, while the ----------------
+            // ---------------- consumers stream the channels of the current one    ----------------
+            const int btid = tid - (kSplitConsumerWarps + 1) * 32;
+            uint32_t tcount = 0;
+            for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++tcount) {
+                const int tx_i = (int)(tile % p.tiles_x);
+                const int ty_i = (int)((tile / p.tiles_x) % p.tiles_y);
+                const long long nz = tile / tiles_per_plane;
+                const int z = p.z0 + (int)(nz % p.ZW), n = (int)(nz / p.ZW);
+                const int x0 = tx_i * TX, y0 = ty_i * TR;
+                split_wait(halo_full, tcount & 1u, abort_flag, p.status, 6);
+                split_fill_rows(p, rows, orows, HSLOT, TXP, gate, btid, n, z, y0, x0);
+                if (tcount) split_wait(m_done, (tcount - 1) & 1u, abort_flag, p.status, 7);  // the previous table has been read
+                tma::named_barrier(3, kSplitBuilders);
+                split_build_table(p, rows, msm, HSLOT, TXP, TS, btid, x0);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the reads of the rows, before TMA rewrites them
+                tma::named_barrier(3, kSplitBuilders);
+                if (btid == 0) {
+                    tma::mbar_arrive(halo_empty);  // the TMA slots may take the next tile's rows
+                    tma::mbar_arrive(table_full);
+                }
+            }
         }
         return;
     }
@@ -251,22 +283,11 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
         const int tfinal = tl + 8 * ((hi ? 2 : 0) + (mid ? 1 : 0));  // the tap whose sum this lane ends up with
         float *wslot = wacc + (size_t)kw * p.C * kSplitWaccPad + tfinal;
         for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++tcount) {
-            const int tx_i = (int)(tile % p.tiles_x);
-            const int ty_i = (int)((tile / p.tiles_x) % p.tiles_y);
-            const long long nz = tile / tiles_per_plane;
-            const int z = p.z0 + (int)(nz % p.ZW), n = (int)(nz / p.ZW);
-            const int x0 = tx_i * TX, y0 = ty_i * TR;
-            split_wait(halo_full, tcount & 1u, abort_flag, p.status, 6);
-            split_fill_rows(p, rows, orows, HSLOT, TXP, gate, tid, n, z, y0, x0);
-            if (tcount) split_wait(m_done, (tcount - 1) & 1u, abort_flag, p.status, 7);
-            tma::named_barrier(1, kSplitConsumers);
-            split_build_table(p, rows, msm, HSLOT, TXP, TS, tid, x0);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            tma::named_barrier(2, kSplitConsumers);
-
 #ifdef MSD_BWD_TIMING
             const long long k0t = clock64();
 #endif
+            split_wait(table_full, tcount & 1u, abort_flag, p.status, 8);
+
             float2 Mk[4][KH / 8];  // [tap of the lane][pair of neighbouring voxels]: operands of packed FMAs
 #pragma unroll
             for (int a = 0; a < 4; ++a) {
@@ -360,23 +381,8 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
             const int z = p.z0 + (int)(nz % p.ZW), n = (int)(nz / p.ZW);
             const int x0 = tx_i * TX, y0 = ty_i * TR;
             MSD_T(t0);
-            split_wait(halo_full, tcount & 1u, abort_flag, p.status, 6);
-            MSD_T(t1);
-            split_fill_rows(p, rows, orows, HSLOT, TXP, gate, tid, n, z, y0, x0);
-            MSD_T(t1a);
-            if (tcount) split_wait(m_done, (tcount - 1) & 1u, abort_flag, p.status, 7);
-            tma::named_barrier(1, kSplitConsumers);
-            MSD_T(t2);
-            split_build_table(p, rows, msm, HSLOT, TXP, TS, tid, x0);
-            MSD_T(t2a);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            MSD_T(t2b);
-            MSD_TADD(10, t2a, t2b);  // the proxy fence
-            tma::named_barrier(2, kSplitConsumers);
-            if (tid == 0) tma::mbar_arrive(halo_empty);  // the TMA slots may take the next tile's rows
+            split_wait(table_full, tcount & 1u, abort_flag, p.status, 8);
             MSD_T(t3);
-            MSD_TADD(8, t1, t1a);   // pass A alone
-            MSD_TADD(9, t2, t2a);   // pass B alone
 
             float2 M[TAPS][2];  // pairs of neighbouring voxels: operands of packed FMAs
             const bool valid = (y0 + r) < p.Y;
@@ -452,9 +458,7 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
                 if (++s == (uint32_t)S) s = 0, ph ^= 1u;
             }
             MSD_T(t5);
-            MSD_TADD(0, t0, t1);  // wait for the halo rows
-            MSD_TADD(1, t1, t2);  // pass A + barrier
-            MSD_TADD(2, t2, t3);  // pass B + barrier
+            MSD_TADD(0, t0, t3);  // wait for the table
             MSD_TADD(3, t3, t4);  // M registers
             MSD_TADD(4, t4, t5);  // channel loop
             MSD_TADD(5, 0, 1);    // tiles
