@@ -55,7 +55,7 @@ constexpr int kSplitMaxStages = 8;
 constexpr int kSplitHeaderBytes = 512;                            // barriers, abort flag, bias slots
 constexpr int kSplitBuilderWarps = 3;                             // warps 13-15
 constexpr int kSplitBuilders = kSplitBuilderWarps * 32;
-constexpr int kSplitRegsX = 192, kSplitRegsP = 64;  // 128 x 192 + 256 x 128 + 128 x 64 = 65536 registers
+constexpr int kSplitRegsX = 176, kSplitRegsP = 80;  // 128 x 176 + 256 x 128 + 128 x 80 = 65536 registers
 
 // Bounded wait with a fast path: one try_wait before the generic bounded loop.
 __device__ __forceinline__ void split_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
