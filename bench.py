@@ -56,10 +56,10 @@ def algorithmic_bytes(depth, voxels):
 # DRAM traffic per launch measured by ncu (dram__bytes_read.sum + dram__bytes_write.sum) divided
 # by the algorithmic bytes of the captured launch: 2D backward 1224.7 / 1275.1 MB and 2D forward
 # 429.6 / 427.8 MB (batch 8 of 512x512, 50 input channels, dilation 10); 3D backward
-# 1238.4 / 1291.8 MB and 3D forward 509.6 / 436.2 MB (batch 2 of 128^3, 25 input channels,
-# dilation 4).  Traffic grows with the channel count like the algorithmic bytes do, so the ratio
+# 2495.1 / 2550.1 MB (batch 2 of 128^3, 50 input channels, dilation 2) and 3D forward
+# 509.6 / 436.2 MB (batch 2 of 128^3, 25 input channels, dilation 4).  Traffic grows with the channel count like the algorithmic bytes do, so the ratio
 # is applied to the average launch.
-NCU_TRAFFIC_RATIO = {("bwd", 2): 1224.7 / 1275.1, ("fwd", 2): 429.6 / 427.8, ("bwd", 3): 1238.4 / 1291.8, ("fwd", 3): 509.6 / 436.2}
+NCU_TRAFFIC_RATIO = {("bwd", 2): 1224.7 / 1275.1, ("fwd", 2): 429.6 / 427.8, ("bwd", 3): 2495.1 / 2550.1, ("fwd", 3): 509.6 / 436.2}
 
 
 def measured_peak():
@@ -322,7 +322,8 @@ def run_ours(args, cfg, rank, world, device):
             "device_status": status,
             "clocks": clocks,
             "roofline": {
-                "kernel": "fused_backward_kernel (one launch per layer; the small second-pass reductions are inside the timed span)",
+                "kernel": ("fused_backward_kernel" if nd == 2 else "fused_backward3d_split_kernel (fused_backward_kernel<3> below 8 input channels)")
+                + " (one launch per layer; the small second-pass reductions are inside the timed span)",
                 "bound": "hbm", "achieved": gbs_bwd, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": gbs_bwd / peak,
                 "frac_of_nominal_8TBs": gbs_bwd / 8000.0,
                 "algorithmic_bytes_per_launch": a_bwd / depth, "avg_launch_ms": ms_bwd / depth, "launches": depth,

@@ -3,7 +3,8 @@
 Replaces the reference's ``benchmarks/benchmark_block_sizes.py`` (a sweep over CUDA thread
 block shapes): here the knobs are the kernels' launch *variants* — tile height / width,
 lattice rows and column segments per thread of the TMA forward, voxels per thread and
-resident blocks of the fused backward.  For a given problem shape the tuner times every
+resident blocks of the fused 2D backward, unsplit or role-split consumer warps of the 3D
+backward.  For a given problem shape the tuner times every
 variant of every (kernel family, dilation) on synthetic data with CUDA events, installs
 the winners in the library's launch table (``msd_tuning_set``) and remembers them in a JSON
 cache keyed by GPU name and shape, so that later processes only look them up.

@@ -151,7 +151,7 @@ def main(args, cfg, rank, world, local, peak=(6650.0, "fallback")):
             "e2e": {"value": st.vox_total / (ms_e2e * 1e-3), "unit": "voxels/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": int(2 * st.vox_rank * 4), "d2h_bytes_per_step": 4},
             "gpu_launches": launches, "device_status": status,
-            "roofline": {"kernel": "fused_backward_kernel<3> (per rank; halo exchanges inside the timed span)", "bound": "hbm",
+            "roofline": {"kernel": "fused_backward3d_split_kernel (per rank; halo exchanges inside the timed span)", "bound": "hbm",
                          "achieved": gbs_bwd, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": gbs_bwd / peak,
                          "algorithmic_bytes_per_launch": a_bwd / st.depth, "avg_launch_ms": ms_bwd / st.depth, "launches": st.depth,
                          "traffic": None},
