@@ -55,8 +55,9 @@ struct BwdPlan {
 
 // geometry of the role-split 3D kernel (the constants of the same names there)
 static const int kSplitRows = 4, kSplitKWarps = 8, kSplitCB = 4, kSplitMaxDilation = 12, kSplitMaxStages = 8, kSplitHeader = 512;
-// below this many input channels the per-tile set-up of the split kernel outweighs its faster channel loop
-static const int kSplitMinChannels = 8;
+// below this many input channels the per-tile set-up of the split kernel outweighs its faster
+// channel loop (large dilations have more border tiles, whose set-up reads global memory)
+static int split_min_channels(int d) { return d <= 5 ? 8 : 12; }
 
 static bool plan(const BackwardArgs &a, BwdPlan *pl) {
     const View &g = *a.gout;
@@ -68,7 +69,7 @@ static bool plan(const BackwardArgs &a, BwdPlan *pl) {
     pl->txq16 = g.x <= 64 ? 1 : 0;
     pl->split = false;
     const int TX = pl->txq16 ? 64 : 128;
-    if (nd == 3 && do_x && do_k && (g.x % 128) == 0 && a.d <= kSplitMaxDilation && C >= kSplitMinChannels && tuning_get(BWD3D, a.d) != 0) {
+    if (nd == 3 && do_x && do_k && (g.x % 128) == 0 && a.d <= kSplitMaxDilation && C >= split_min_channels(a.d) && tuning_get(BWD3D, a.d) != 0) {
         // role-split kernel: 4 X warps + 8 K warps on tiles of 4 rows x 128 columns, kSplitCB
         // channels per ring stage; the table of M (27 taps x (4 x 128 + 4) floats) beside the halo rows
         const int TR = kSplitRows, TXP = 128 + 2 * Dp;
