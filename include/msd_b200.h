@@ -179,13 +179,25 @@ MSD_API size_t msd_final_workspace_bytes(int64_t c_in, int64_t c_out);
  * block on a z-slab: `buffer[N, C, Zl, Y, X]` (float32) is this GPU's part of the dense
  * buffer, its planes [z_begin, z_end) owned, the planes below/above them halo copies of
  * the neighbours' planes (at least `dilation` of them, except at the volume's real ends,
- * where the buffer ends too and the edge-inclusive reflection applies).  Reads channels
- * [0, n_in) on owned + halo planes, writes channel n_in on the owned planes only.  The
- * caller exchanges that channel's boundary planes afterwards.  Needs the workspace of
- * msd_forward_workspace_bytes() for the whole local buffer. */
+ * where the buffer ends too and the edge-inclusive reflection applies).  Writes channel
+ * n_in on the owned planes only.  Needs the workspace of msd_forward_workspace_bytes() for
+ * the whole local buffer: it holds the three z-tap partial sums u[3][N][Zl][Y][X]
+ * (u_t[z] = the in-plane 3x3 sum of plane z with the weights of z-tap t), from which
+ * out[z] = relu(bias + u_0[z - d] + u_1[z] + u_2[z + d]).
+ * `flags` = 0: both steps in one call; the partial sums are computed on the window widened
+ * by `dilation` planes, which reads channels [0, n_in) on halo planes (the caller has
+ * exchanged them) and repeats work of the neighbours.
+ * `flags` = MSD_SLAB_FORWARD_SUMS_ONLY: only the partial sums, on exactly [z_begin, z_end)
+ * (any sub-window of the owned planes; no halo plane of the input is read).
+ * `flags` = MSD_SLAB_FORWARD_GATHER_ONLY: only the second step on [z_begin, z_end); the
+ * caller has filled u_0 on the `dilation` planes below the owned ones and u_2 on the
+ * `dilation` planes above them with the neighbours' partial sums (planes of the same
+ * global index), so no layer ever needs an activation halo. */
+#define MSD_SLAB_FORWARD_SUMS_ONLY 1
+#define MSD_SLAB_FORWARD_GATHER_ONLY 2
 MSD_API int msd_slab_layer_forward(const msd_tensor_t *buffer, int n_in, const void *weight, const void *bias,
-                           int dilation, int z_begin, int z_end, void *workspace, size_t workspace_bytes,
-                           int device, void *stream);
+                           int dilation, int z_begin, int z_end, int flags, void *workspace,
+                           size_t workspace_bytes, int device, void *stream);
 
 /* Backward of the same layer on the slab: uses channel n_in of `result` (gate) and of
  * `gradients` on owned + halo planes (the caller has exchanged the gradient halo), adds the
@@ -226,13 +238,15 @@ MSD_API int msd_tuning_get(int family, int dilation);
  * backward) rather than the generic one. */
 MSD_API int64_t msd_launch_count(void);
 MSD_API int64_t msd_fast_launch_count(void);
+MSD_API int64_t msd_split_launch_count(void); /* of those, launches of the role-split 3D backward kernel */
 MSD_API void msd_reset_launch_count(void);
 
 /* No counterpart in the reference: msd_conv_relu_backward_k for callers that cannot
  * allocate device memory (a plugin inside another framework's memory pool, a latency-bound
  * serving loop, a host with a fixed memory plan).  It takes no workspace: the partial sums
  * live in a 4 MiB array built into the library, which every GPU that loads the library
- * holds until exit.  Shapes that need more return MSD_ERR_LIMIT and launch nothing.  All
+ * holds until exit.  Shapes that need more return MSD_ERR_LIMIT and launch nothing (for
+ * one output channel: more than 356 input channels in 2D, more than 118 in 3D).  All
  * calls on a device share the array, so calls that may overlap on the GPU race; calls on
  * one stream are safe.  The first call on each device resolves the array's address and
  * should be made outside any stream capture.  Allocates nothing. */
@@ -248,6 +262,15 @@ MSD_API size_t msd_noalloc_scratch_bytes(void);
  * ran out (the affected call's results are then invalid).  The tuned kernels never spin
  * without a limit, so a protocol error shows up here instead of as a hung GPU. */
 MSD_API int msd_device_status(int device, void *stream, int *status_out);
+
+/* No counterpart in the reference: self-test of the bounded-wait machinery.  Launches one
+ * small block that waits on an mbarrier nobody ever arrives at, with a time limit of
+ * `limit_ns` nanoseconds (1000 .. 10^9) on the GPU's timer.  The wait runs out by itself,
+ * the kernel returns normally and leaves MSD_STATUS_SELFTEST_TIMEOUT in the device status
+ * word, which msd_device_status() then reports and clears.  Nothing traps, faults or
+ * spins without a limit; the context stays usable. */
+#define MSD_STATUS_SELFTEST_TIMEOUT 99
+MSD_API int msd_selftest_wait_timeout(uint64_t limit_ns, int device, void *stream);
 
 #ifdef __cplusplus
 }

@@ -18,6 +18,7 @@ MAX_DIMS = 5
 
 FAMILY_FWD2D, FAMILY_BWD2D, FAMILY_FWD3D, FAMILY_BWD3D = 0, 1, 2, 3
 SLAB_GRADIENT_IS_GATED, SLAB_GATE_CHANNEL_BELOW = 1, 2
+SLAB_FORWARD_SUMS_ONLY, SLAB_FORWARD_GATHER_ONLY = 1, 2
 
 
 class MsdTensor(ctypes.Structure):
@@ -58,17 +59,19 @@ def _load():
         "msd_final_forward": (i, [i, T, vp, vp, T, i, vp]),
         "msd_final_backward": (i, [i, T, T, vp, T, vp, vp, vp, sz, i, vp]),
         "msd_final_workspace_bytes": (sz, [i64, i64]),
-        "msd_slab_layer_forward": (i, [T, i, vp, vp, i, i, i, vp, sz, i, vp]),
+        "msd_slab_layer_forward": (i, [T, i, vp, vp, i, i, i, i, vp, sz, i, vp]),
         "msd_slab_layer_backward": (i, [T, T, i, vp, i, i, i, vp, vp, i, vp, sz, i, vp]),
         "msd_tuning_num_variants": (i, [i]),
         "msd_tuning_set": (i, [i, i, i]),
         "msd_tuning_get": (i, [i, i]),
         "msd_launch_count": (i64, []),
         "msd_fast_launch_count": (i64, []),
+        "msd_split_launch_count": (i64, []),
         "msd_reset_launch_count": (None, []),
         "msd_device_status": (i, [i, vp, ctypes.POINTER(ctypes.c_int)]),
         "msd_conv_relu_backward_k_noalloc": (i, [i, T, T, T, vp, i, i, vp]),
         "msd_noalloc_scratch_bytes": (sz, []),
+        "msd_selftest_wait_timeout": (i, [ctypes.c_uint64, i, vp]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)
@@ -86,8 +89,8 @@ EXPORTED = [
     "msd_slab_layer_forward", "msd_slab_layer_backward",
     "msd_final_forward", "msd_final_backward", "msd_final_workspace_bytes",
     "msd_tuning_num_variants", "msd_tuning_set", "msd_tuning_get",
-    "msd_launch_count", "msd_fast_launch_count", "msd_reset_launch_count", "msd_device_status",
-    "msd_conv_relu_backward_k_noalloc", "msd_noalloc_scratch_bytes",
+    "msd_launch_count", "msd_fast_launch_count", "msd_split_launch_count", "msd_reset_launch_count", "msd_device_status",
+    "msd_conv_relu_backward_k_noalloc", "msd_noalloc_scratch_bytes", "msd_selftest_wait_timeout",
 ]
 
 

@@ -4,6 +4,7 @@
 #include <string.h>
 #include "common.cuh"
 #include "kernels.h"
+#include "tma.cuh"
 
 namespace msd {
 
@@ -16,11 +17,12 @@ void set_error(const char *fmt, ...) {
     va_end(ap);
 }
 
-static std::atomic<int64_t> g_launches{0}, g_fast_launches{0};
+static std::atomic<int64_t> g_launches{0}, g_fast_launches{0}, g_split_launches{0};
 void count_launch(bool fast) {
     g_launches.fetch_add(1, std::memory_order_relaxed);
     if (fast) g_fast_launches.fetch_add(1, std::memory_order_relaxed);
 }
+void count_split_launch() { g_split_launches.fetch_add(1, std::memory_order_relaxed); }
 
 static bool same_geometry(const View &a, const View &b) { return a.n == b.n && a.z == b.z && a.y == b.y && a.x == b.x; }
 
@@ -231,6 +233,7 @@ int msd_block_forward(int dtype, const msd_tensor_t *result, int c_in, int depth
     MSD_CUDA_TRY(g.status);
     cudaStream_t s = (cudaStream_t)stream;
     const size_t es = dtype == MSD_F64 ? 8 : 4;
+    tma::OverlapScope overlap;  // the first kernel is launched the ordinary way, the later layers may overlap their predecessor
     for (int i = 0; i < depth; ++i) {
         const int64_t n_i = c_in + (int64_t)i * width;
         View in = channel_slice(r, 0, n_i, es);
@@ -242,6 +245,7 @@ int msd_block_forward(int dtype, const msd_tensor_t *result, int c_in, int depth
         else
             rc = generic::forward(dtype, true, in, weights[i], b, out, nd, d, s);
         if (rc) return rc;
+        tma::set_overlap_allowed(true);
     }
     return MSD_OK;
 }
@@ -277,38 +281,64 @@ int msd_block_backward(int dtype, const msd_tensor_t *result, const msd_tensor_t
     // `gated`: the gradient channel the next layer reads is already multiplied by that layer's
     // ReLU gate (done by the kernel of the layer above when it stores that channel), so the
     // layer's kernel needs no halo of the activation.  The topmost channel is gated up front.
+    // A layer hands its gradient over gated only when the layer below will run the tuned
+    // kernel as well (checked one layer ahead, with that layer's own arguments).
     bool gated = false;
+    const bool fast_dtype = dtype == MSD_F32 && width == 1;
+    tma::OverlapScope overlap;  // see msd_block_forward
+    auto layer_args = [&](int i, View *out, View *gout, View *in, View *gin) {
+        const int64_t n_i = c_in + (int64_t)i * width;
+        *out = channel_slice(r, n_i, width, es);
+        *in = channel_slice(r, 0, n_i, es);
+        *gout = channel_slice(gr, n_i, width, es);
+        *gin = channel_slice(gr, 0, n_i, es);
+        return fast::BackwardArgs{out, gout, in, gin, (const float *)weights[i], grad_weights ? (float *)grad_weights[i] : nullptr,
+                                  grad_bias ? (float *)grad_bias + i : nullptr, nd, dilations[i], workspace, workspace_bytes, &pending, -1};
+    };
     for (int i = depth - 1; i >= 0; --i) {
         const int64_t n_i = c_in + (int64_t)i * width;
-        View out = channel_slice(r, n_i, width, es);
-        View in = channel_slice(r, 0, n_i, es);
-        View gout = channel_slice(gr, n_i, width, es);
-        View gin = channel_slice(gr, 0, n_i, es);
+        View out, gout, in, gin;
         const int d = dilations[i];
         void *gk = grad_weights ? grad_weights[i] : nullptr;
         void *gb = grad_bias ? (char *)grad_bias + (size_t)i * width * es : nullptr;
-        if (dtype == MSD_F32 && width == 1) {
-            // gate the channel below on store when that layer will run the fused kernel too
-            const bool can_gate_next = gk != nullptr && i > 0 && n_i - 1 >= c_in;
-            fast::BackwardArgs a{&out, &gout, &in, &gin, (const float *)weights[i], (float *)gk, (float *)gb, nd, d, workspace, workspace_bytes,
-                                 &pending, can_gate_next ? (int)(n_i - 1) : -1};
+        if (fast_dtype) {
+            fast::BackwardArgs a = layer_args(i, &out, &gout, &in, &gin);
+            // the topmost gradient channel can be gated in place before the first layer runs
+            const bool gate_first = !gated && i == depth - 1 && fast::gate_channel_supported(gout, out);
+            if (gated || gate_first) a.out = nullptr;  // eligibility is judged with the halo buffers this launch will really use
             if (fast::backward_supported(a)) {
-                if (!gated && i == depth - 1 && fast::gate_channel_supported(gout, out)) {
+                bool can_gate_next = false;
+                if (gk != nullptr && i > 0) {
+                    View o2, go2, in2, gi2;
+                    fast::BackwardArgs below = layer_args(i - 1, &o2, &go2, &in2, &gi2);
+                    below.out = nullptr;  // what that layer would be given after a gated hand-over
+                    can_gate_next = fast::backward_supported(below);
+                }
+                a.mask_channel = can_gate_next ? (int)(n_i - 1) : -1;
+                if (gate_first) {
                     if ((rc = fast::gate_channel(gout, out, device, s))) return rc;
                     gated = true;
                 }
-                if (gated) a.out = nullptr;
                 if ((rc = fast::backward(a, device, s))) return rc;
+                tma::set_overlap_allowed(true);
                 gated = can_gate_next;
                 continue;
             }
+        } else {
+            out = channel_slice(r, n_i, width, es), in = channel_slice(r, 0, n_i, es);
+            gout = channel_slice(gr, n_i, width, es), gin = channel_slice(gr, 0, n_i, es);
         }
         // the generic kernels use the workspace from its start: finish pending reductions first
         if ((rc = fast::flush_reductions(&pending, s))) return rc;
-        if (gated) MSD_FAIL(MSD_ERR_UNSUPPORTED, "msd_block_backward: layer %d cannot run the tuned kernel after the layer above gated its gradient", i);
-        if ((rc = generic::backward_x(dtype, true, &out, gout, weights[i], gin, nd, d, s))) return rc;
-        if (gk && (rc = generic::backward_k(dtype, true, &out, gout, in, gk, nd, d, workspace, workspace_bytes, s))) return rc;
-        if (gb && (rc = generic::backward_bias(dtype, true, &out, gout, gb, workspace, workspace_bytes, s))) return rc;
+        // A gradient that arrived already gated must not be gated again from `out`; the look-ahead
+        // above keeps this from happening, the un-gated kernels are the safe answer if it ever does.
+        const bool relu = !gated;
+        const View *gate = relu ? &out : nullptr;
+        if ((rc = generic::backward_x(dtype, relu, gate, gout, weights[i], gin, nd, d, s))) return rc;
+        if (gk && (rc = generic::backward_k(dtype, relu, gate, gout, in, gk, nd, d, workspace, workspace_bytes, s))) return rc;
+        if (gb && (rc = generic::backward_bias(dtype, relu, gate, gout, gb, workspace, workspace_bytes, s))) return rc;
+        tma::set_overlap_allowed(true);
+        gated = false;
     }
     return fast::flush_reductions(&pending, s);
 }
@@ -323,18 +353,23 @@ static int slab_checks(const char *op, const msd_tensor_t *buffer, int n_in, int
 }
 
 int msd_slab_layer_forward(const msd_tensor_t *buffer, int n_in, const void *weight, const void *bias, int dilation, int z_begin, int z_end,
-                           void *workspace, size_t workspace_bytes, int device, void *stream) {
+                           int flags, void *workspace, size_t workspace_bytes, int device, void *stream) {
     View r;
     int rc = slab_checks("msd_slab_layer_forward", buffer, n_in, dilation, z_begin, z_end, &r);
     if (rc) return rc;
     if (!weight || !bias) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "msd_slab_layer_forward: weight and bias must not be null");
+    if (flags != 0 && flags != MSD_SLAB_FORWARD_SUMS_ONLY && flags != MSD_SLAB_FORWARD_GATHER_ONLY)
+        MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "msd_slab_layer_forward: flags must be 0, MSD_SLAB_FORWARD_SUMS_ONLY or MSD_SLAB_FORWARD_GATHER_ONLY");
     DeviceGuard g(device);
     MSD_CUDA_TRY(g.status);
     View in = channel_slice(r, 0, n_in, 4), out = channel_slice(r, n_in, 1, 4);
     if (!fast::forward_supported(in, out, 3, dilation, workspace, workspace_bytes))
         MSD_FAIL(MSD_ERR_UNSUPPORTED, "msd_slab_layer_forward: shape, alignment, dilation (1..10) or workspace not supported by the tuned 3D kernel");
     fast::set_z_window(z_begin, z_end);
+    fast::set_forward_phase(flags == MSD_SLAB_FORWARD_SUMS_ONLY ? fast::FWD_SUMS_ONLY : flags == MSD_SLAB_FORWARD_GATHER_ONLY ? fast::FWD_GATHER_ONLY
+                                                                                                                               : fast::FWD_BOTH);
     rc = fast::forward(true, in, (const float *)weight, (const float *)bias, out, 3, dilation, workspace, workspace_bytes, device, (cudaStream_t)stream);
+    fast::set_forward_phase(fast::FWD_BOTH);
     fast::set_z_window(0, 0);
     return rc;
 }
@@ -408,9 +443,11 @@ int msd_tuning_get(int family, int dilation) { return fast::tuning_get(family, d
 
 int64_t msd_launch_count(void) { return g_launches.load(); }
 int64_t msd_fast_launch_count(void) { return g_fast_launches.load(); }
+int64_t msd_split_launch_count(void) { return g_split_launches.load(); }
 void msd_reset_launch_count(void) {
     g_launches.store(0);
     g_fast_launches.store(0);
+    g_split_launches.store(0);
 }
 
 }  // extern "C"

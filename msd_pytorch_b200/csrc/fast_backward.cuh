@@ -38,16 +38,6 @@
 #include "kernels.h"
 #include "tma.cuh"
 
-#ifdef MSD_BWD_TIMING
-// Developer instrumentation (off in normal builds): per-phase clock sums of block 0, thread 0.
-#define MSD_T(var) const long long var = clock64()
-#define MSD_TADD(slot, a, b) \
-    if (blockIdx.x == 0 && threadIdx.x == 0 && p.timing) p.timing[slot] += (unsigned long long)((b) - (a))
-#else
-#define MSD_T(var)
-#define MSD_TADD(slot, a, b)
-#endif
-
 namespace msd {
 namespace fast {
 
@@ -78,7 +68,6 @@ struct BwdParams {
     int stages;
     int mask_channel;  // input channel whose new gradient is stored already gated by in[c] > 0 (-1: none)
     int *status;
-    unsigned long long *timing;  // developer instrumentation, null in normal builds
 };
 
 template <int ND>
@@ -303,9 +292,7 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
         const int x0 = tx_i * TX, y0 = ty_i * TR;
 
         // ---- turn the halo rows (landed by TMA) into the folded rows of m, in place ----
-        MSD_T(t0);
         tma::wait_parity(halo_full, tcount & 1u, abort_flag, p.status, 6);
-        MSD_T(t1);
         const float *go_n = p.gout + n * p.go_sn;
         const float *out_n = gate ? p.out + n * p.out_sn : nullptr;
         const int quads = TXP / 4;
@@ -354,9 +341,7 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
             }
             *reinterpret_cast<float4 *>(rows + soff) = g;
         }
-        MSD_T(t2);
         tma::named_barrier(1, kConsumers);
-        MSD_T(t3);
 
         // ---- per-thread M_t for its P voxels ----
         float M[TAPS][P];
@@ -437,7 +422,6 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
         // ---- stream the C input channels past the registers ----
         // CU channels are processed per iteration so that their FMA blocks and shuffle
         // reduce-scatters (long dependent chains) interleave.
-        MSD_T(t4);
         auto body = [&](auto cu_tag, int c) {
             constexpr int CU = decltype(cu_tag)::value;
             float4 a[CU][J], g[CU][J];
@@ -524,13 +508,6 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
             for (; c + CUMAX <= p.C; c += CUMAX) body(std::integral_constant<int, CUMAX>{}, c);
             for (; c < p.C; ++c) body(std::integral_constant<int, 1>{}, c);
         }
-        MSD_T(t5);
-        MSD_TADD(0, t0, t1);  // barrier at tile start
-        MSD_TADD(1, t1, t2);  // staging of the folded rows
-        MSD_TADD(2, t2, t3);  // barrier after staging
-        MSD_TADD(3, t3, t4);  // M registers
-        MSD_TADD(4, t4, t5);  // channel loop
-        MSD_TADD(5, 0, 1);    // tiles
     }
 
     // ---- block epilogue: fixed-order sums of the warp slots, one partial per block ----
@@ -560,7 +537,7 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
     }
 }
 
-// Host-side launcher of one instantiation; defined in fast_backward_impl.cuh.
+// Host-side launcher of one instantiation (defined in fast_backward_2d.cu / fast_backward_3d.cu).
 typedef int (*BwdLaunchFn)(const CUtensorMap *maps, const BwdParams &, int grid, size_t smem, cudaStream_t);  // maps: in, gin, gout, out
 
 }  // namespace fast

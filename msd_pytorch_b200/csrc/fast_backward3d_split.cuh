@@ -5,11 +5,11 @@
 //   X warps  voxels across lanes (4 consecutive x per thread), the 27 values M_t of each
 //            voxel in registers: per channel 27 x 4 FMAs update the input gradient, one
 //            128-bit store.  No reduction of any kind.
-//   K warps  the 27 TAPS across lanes: lane t keeps M_t[v] for the 64 voxels v of half a tile
-//            row in registers and reads in[c][v] with broadcast 128-bit shared loads, so
-//            that it accumulates  sum_v in[c][v] * M_t[v]  all by itself.  The weight gradient
-//            needs NO cross-lane reduction (the shuffle reduce-scatter of the unsplit kernel
-//            costs 124 instructions per 216 FMAs in 3D); lanes 27..31 idle.
+//   K warps  lane = (quarter-warp, tap lane): each lane keeps M_t[v] for 4 taps (tap lane + 8 a)
+//            and 16 voxels of half a tile row in registers, reads in[c][v] with 128-bit
+//            shared loads and accumulates  sum_v in[c][v] * M_t[v]  with packed FMAs; the
+//            four quarter-warps' sums meet in a 3-shuffle reduce-scatter (the full shuffle
+//            tree of the unsplit kernel costs 124 instructions per 216 FMAs in 3D).
 //
 // A tile is 4 rows x 128 columns of one z-plane.  The block has four warpgroups:
 //   warps 0-3    X warps, one per tile row               (registers raised to kSplitRegsX)
@@ -283,9 +283,6 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
         const int tfinal = tl + 8 * ((hi ? 2 : 0) + (mid ? 1 : 0));  // the tap whose sum this lane ends up with
         float *wslot = wacc + (size_t)kw * p.C * kSplitWaccPad + tfinal;
         for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++tcount) {
-#ifdef MSD_BWD_TIMING
-            const long long k0t = clock64();
-#endif
             split_wait(table_full, tcount & 1u, abort_flag, p.status, 8);
 
             float2 Mk[4][KH / 8];  // [tap of the lane][pair of neighbouring voxels]: operands of packed FMAs
@@ -302,19 +299,9 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
             }
             __syncwarp();
             if (lane == 0) tma::mbar_arrive(m_done);
-#ifdef MSD_BWD_TIMING
-            if (blockIdx.x == 0 && tid == 128 && p.timing) p.timing[11] += (unsigned long long)(clock64() - k0t);  // K warp 0: M registers
-            const long long k1t = clock64();
-#endif
 
             for (int g = 0; g < ngroups; ++g) {
-#ifdef MSD_BWD_TIMING
-                const long long w0 = clock64();
-#endif
                 split_wait(&full[s], ph, abort_flag, p.status, 2);
-#ifdef MSD_BWD_TIMING
-                if (blockIdx.x == 0 && tid == 128 && p.timing) p.timing[7] += (unsigned long long)(clock64() - w0);  // K warp 0: waiting for a stage
-#endif
                 const float4 *ain0 = reinterpret_cast<const float4 *>(ring + s * STAGE + r * TX + KH * h) + qw;  // in[g * CB], this half row
                 float tot[CB];
                 // two channels at a time: eight independent chains of packed FMAs, and one
@@ -365,9 +352,6 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
                 }
                 if (++s == (uint32_t)S) s = 0, ph ^= 1u;
             }
-#ifdef MSD_BWD_TIMING
-            if (blockIdx.x == 0 && tid == 128 && p.timing) p.timing[12] += (unsigned long long)(clock64() - k1t);  // K warp 0: channel loop
-#endif
         }
     } else {
         // ===================================== X warps =====================================
@@ -380,9 +364,7 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
             const long long nz = tile / tiles_per_plane;
             const int z = p.z0 + (int)(nz % p.ZW), n = (int)(nz / p.ZW);
             const int x0 = tx_i * TX, y0 = ty_i * TR;
-            MSD_T(t0);
             split_wait(table_full, tcount & 1u, abort_flag, p.status, 8);
-            MSD_T(t3);
 
             float2 M[TAPS][2];  // pairs of neighbouring voxels: operands of packed FMAs
             const bool valid = (y0 + r) < p.Y;
@@ -396,12 +378,8 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
             if (lane == 0) tma::mbar_arrive(m_done);
 
             float *gi_row = p.gin + n * p.gi_sn + z * p.gi_sz + (int64_t)(y0 + r) * p.gi_sy + x0 + 4 * xq;
-            MSD_T(t4);
             for (int g = 0; g < ngroups; ++g) {
-                MSD_T(w0);
                 split_wait(&full[s], ph, abort_flag, p.status, 2);
-                MSD_T(w1);
-                MSD_TADD(6, w0, w1);  // X warp 0: waiting for a stage
                 const float *stage = ring + s * STAGE + r * TX + 4 * xq;
                 const bool live = valid && !*abort_flag;
                 // two channels at a time: eight independent FMA chains that share the M operands.
@@ -457,11 +435,6 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
                 if (lane == 0) tma::mbar_arrive(&empty[s]);
                 if (++s == (uint32_t)S) s = 0, ph ^= 1u;
             }
-            MSD_T(t5);
-            MSD_TADD(0, t0, t3);  // wait for the table
-            MSD_TADD(3, t3, t4);  // M registers
-            MSD_TADD(4, t4, t5);  // channel loop
-            MSD_TADD(5, 0, 1);    // tiles
         }
         if (p.part_b) {
 #pragma unroll

@@ -13,16 +13,6 @@ extern BwdLaunchFn bwd2d_launchers[2][2][3];
 extern BwdLaunchFn bwd3d_launchers[2][3];
 extern BwdLaunchFn bwd3d_split_launcher;
 
-#ifdef MSD_BWD_TIMING
-static unsigned long long *g_dbg_timing = nullptr;
-extern "C" MSD_API void msd_debug_bwd_timing(unsigned long long *out) {
-    cudaDeviceSynchronize();
-    if (g_dbg_timing) {
-        cudaMemcpy(out, g_dbg_timing, 128, cudaMemcpyDeviceToHost);
-        cudaMemset(g_dbg_timing, 0, 128);
-    }
-}
-#endif
 
 static const int kMaxFastDilation = 16;
 static const size_t kSmemBudget = 220 * 1024;
@@ -262,17 +252,6 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
     p.mask_channel = (do_x && do_k) ? a.mask_channel : -1;
     p.status = tma::device_status_ptr(device);
     if (!p.status) MSD_FAIL(MSD_ERR_CUDA, "fused backward: cannot locate the device status word");
-#ifdef MSD_BWD_TIMING
-    {
-        static unsigned long long *dbg = nullptr;
-        if (!dbg) {
-            cudaMalloc(&dbg, 128);
-            cudaMemset(dbg, 0, 128);
-        }
-        p.timing = dbg;
-        g_dbg_timing = dbg;
-    }
-#endif
     int grid = sm_count(device) * pl.blocks_per_sm;
     if (grid > kMaxGrid) grid = kMaxGrid;
     if (p.num_tiles < grid) grid = (int)p.num_tiles;
@@ -313,6 +292,7 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
     int rc = fn(maps, p, grid, pl.smem, s);
     if (rc) return rc;
     count_launch(true);
+    if (pl.split) count_split_launch();
     if (do_k || do_b) {
         ReduceList single;
         ReduceList *list = a.defer ? a.defer : &single;

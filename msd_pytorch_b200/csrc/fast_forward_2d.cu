@@ -143,7 +143,15 @@ static const Fwd2dVariant kFwd3d[10][2] = {
 
 static const size_t kFwdSmemBudget = 220 * 1024;
 
-int num_forward2d_variants() { return kNumFwd2dVariants; }
+int num_variants(int family) {
+    switch (family) {
+        case FWD2D: return kNumFwd2dVariants;  // lattice rows x column segments x tile width
+        case BWD2D: return 2;  // 4 / 8 voxels per thread
+        case FWD3D: return 2;  // 4 / 2 column segments per thread
+        case BWD3D: return 2;  // unsplit consumers / X warps + K warps
+        default: return 1;
+    }
+}
 
 static bool fwd_plan(const View &in, int nd, int d, const Fwd2dVariant **var, int *stages) {
     if (d < 1 || d > 10) return false;
@@ -166,7 +174,7 @@ static bool fwd_plan(const View &in, int nd, int d, const Fwd2dVariant **var, in
 
 size_t forward_workspace_bytes(int nd, int64_t voxels) { return nd == 3 ? (size_t)voxels * 3 * sizeof(float) + 256 : 0; }
 
-bool forward_nd_supported(const View &in, const View &out, int nd, int d, const void *ws, size_t wsb) {
+bool forward_supported(const View &in, const View &out, int nd, int d, const void *ws, size_t wsb) {
     if (out.c != 1 || in.c < 1 || in.c > 4096) return false;
     if (in.sx != 1 || out.sx != 1) return false;
     // TMA: 16-byte aligned base and strides
@@ -183,7 +191,7 @@ bool forward_nd_supported(const View &in, const View &out, int nd, int d, const 
     return fwd_plan(in, nd, d, &var, &stages);
 }
 
-int forward_nd(bool relu, const View &in, const float *k, const float *bias, const View &out, int nd, int d, void *ws, size_t wsb, int device,
+int forward(bool relu, const View &in, const float *k, const float *bias, const View &out, int nd, int d, void *ws, size_t wsb, int device,
                cudaStream_t s) {
     const Fwd2dVariant *var;
     int stages;
@@ -216,7 +224,8 @@ int forward_nd(bool relu, const View &in, const float *k, const float *bias, con
     p.N = (int)in.n, p.C = (int)in.c, p.Z = (int)in.z, p.Y = (int)in.y, p.X = (int)in.x;
     get_z_window((int)in.z, &p.z0, &p.ZW);
     const int gather_z0 = p.z0, gather_zw = p.ZW;
-    if (nd == 3) {
+    const int phase = nd == 3 ? get_forward_phase() : FWD_BOTH;
+    if (nd == 3 && phase == FWD_BOTH) {
         // the z-gather of plane z reads the partial sums of planes z - d and z + d: compute
         // those for the window widened by d on both sides (clipped to the local buffer)
         const int lo = p.z0 - d < 0 ? 0 : p.z0 - d;
@@ -230,12 +239,14 @@ int forward_nd(bool relu, const View &in, const float *k, const float *bias, con
     p.relu = relu ? 1 : 0;
     p.status = tma::device_status_ptr(device);
     if (!p.status) MSD_FAIL(MSD_ERR_CUDA, "forward: cannot locate the device status word");
-    int grid = sm_count(device);
-    if (p.num_tiles < grid) grid = (int)p.num_tiles;
-    rc = var->launch(map, p, grid, stages, s);
-    if (rc) return rc;
-    count_launch(true);
-    if (nd == 3) {
+    if (phase != FWD_GATHER_ONLY) {
+        int grid = sm_count(device);
+        if (p.num_tiles < grid) grid = (int)p.num_tiles;
+        rc = var->launch(map, p, grid, stages, s);
+        if (rc) return rc;
+        count_launch(true);
+    }
+    if (nd == 3 && phase != FWD_SUMS_ONLY) {
         const int64_t quads = in.n * (int64_t)gather_zw * in.y * in.x / 4;
         int64_t g = ceil_div(quads, 256);
         const int64_t gmax = (int64_t)sm_count(device) * 16;

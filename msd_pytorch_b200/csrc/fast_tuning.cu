@@ -3,6 +3,7 @@
 // records the winners here through msd_tuning_set().
 #include <mutex>
 #include "kernels.h"
+#include "tma.cuh"
 
 namespace msd {
 namespace fast {
@@ -37,6 +38,10 @@ static thread_local int t_z0 = 0, t_z1 = 0;
 
 void set_z_window(int z0, int z1) { t_z0 = z0, t_z1 = z1; }
 
+static thread_local int t_phase = FWD_BOTH;
+void set_forward_phase(int phase) { t_phase = phase; }
+int get_forward_phase() { return t_phase; }
+
 void get_z_window(int Z, int *z0, int *zw) {
     if (t_z1 > t_z0 && t_z0 >= 0 && t_z1 <= Z) {
         *z0 = t_z0;
@@ -48,4 +53,10 @@ void get_z_window(int Z, int *z0, int *zw) {
 }
 
 }  // namespace fast
+
+namespace tma {
+static thread_local bool t_overlap = false;
+bool overlap_allowed() { return t_overlap; }
+void set_overlap_allowed(bool on) { t_overlap = on; }
+}  // namespace tma
 }  // namespace msd

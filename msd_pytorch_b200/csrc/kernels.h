@@ -25,6 +25,13 @@ enum Family { FWD2D = 0, BWD2D = 1, FWD3D = 2, BWD3D = 3, NUM_FAMILIES = 4 };
 // halo.  Used by the slab entry points of the C ABI; cleared again before they return.
 void set_z_window(int z0, int z1);
 void get_z_window(int Z, int *z0, int *zw);
+// Which half of the two-kernel 3D forward the calling thread's next forward() runs: both (the
+// z-tap partial sums on the window widened by the dilation, then the z-gather), only the
+// partial sums on exactly the window, or only the z-gather of the window.  The slab entry
+// point uses the halves so that neighbouring slabs can exchange partial sums in between.
+enum ForwardPhase { FWD_BOTH = 0, FWD_SUMS_ONLY = 1, FWD_GATHER_ONLY = 2 };
+void set_forward_phase(int phase);
+int get_forward_phase();
 int num_variants(int family);
 int tuning_set(int family, int dilation, int variant);
 int tuning_get(int family, int dilation);

@@ -15,13 +15,18 @@
 //
 // Consequences the caller must know:
 //  * Shapes whose partial sums need more than the fixed array are refused with
-//    MSD_ERR_LIMIT (the message states both numbers); nothing is launched.  In practice
-//    that is c_in up to about 440 channels in 2D and 149 in 3D for one output channel.
+//    MSD_ERR_LIMIT (the message states both numbers); nothing is launched.  The need is
+//    what msd_workspace_bytes() reports; for float32 and one output channel it is 320
+//    blocks x (c_in x taps + 64) floats + 512 bytes, which fits for c_in <= 356 in 2D
+//    (9 taps) and c_in <= 118 in 3D (27 taps).
 //  * All calls on a device share the one array.  Two calls that may overlap on the GPU
 //    (different streams, no ordering between them) race on it; calls on one stream are
 //    ordered and therefore safe.
 //  * The array keeps whatever the previous call left there.  Nothing has to be cleared:
-//    pass one overwrites every partial that pass two reads.
+//    pass one overwrites every partial that pass two reads.  The one exception: a block
+//    whose bounded wait ran out skips its store, so after a call that left a non-zero
+//    msd_device_status() the gradient may contain leftovers of an earlier call and must
+//    be discarded like every other result of that call.
 //  * The first call on each device looks up the array's device address (a host-side
 //    runtime query, no allocation).  Make that first call outside any stream capture.
 //  * No cudaMalloc, cudaFree or allocating library routine is called on this path.

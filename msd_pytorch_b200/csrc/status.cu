@@ -24,6 +24,19 @@ int *device_status_ptr(int device) {
     return g_ptr[device];
 }
 
+// One warp waits on a barrier that nobody arrives at; see msd_selftest_wait_timeout.
+__global__ void __launch_bounds__(32) wait_timeout_selftest_kernel(int *status, uint64_t limit_ns, int code) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        abort_flag = 0;
+        fence_barrier_init();
+    }
+    __syncwarp();
+    wait_parity(&bar, 0, &abort_flag, status, code, limit_ns);
+}
+
 }  // namespace tma
 }  // namespace msd
 
@@ -40,5 +53,17 @@ extern "C" MSD_API int msd_device_status(int device, void *stream, int *status_o
     MSD_CUDA_TRY(cudaStreamSynchronize(s));
     if (v != 0) MSD_CUDA_TRY(cudaMemsetAsync(p, 0, sizeof(int), s));
     *status_out = v;
+    return MSD_OK;
+}
+
+extern "C" MSD_API int msd_selftest_wait_timeout(uint64_t limit_ns, int device, void *stream) {
+    using namespace msd;
+    if (limit_ns < 1000 || limit_ns > 1000000000ull) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "msd_selftest_wait_timeout: limit_ns must lie in [1e3, 1e9]");
+    DeviceGuard g(device);
+    MSD_CUDA_TRY(g.status);
+    int *p = tma::device_status_ptr(device);
+    if (!p) MSD_FAIL(MSD_ERR_CUDA, "msd_selftest_wait_timeout: cannot locate the status word");
+    tma::wait_timeout_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(p, limit_ns, MSD_STATUS_SELFTEST_TIMEOUT);
+    MSD_CUDA_TRY(cudaGetLastError());
     return MSD_OK;
 }

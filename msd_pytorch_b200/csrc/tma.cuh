@@ -2,9 +2,9 @@
 // kernels: mbarriers, 1-D bulk copies (cp.async.bulk) and tiled TMA loads
 // (cp.async.bulk.tensor).  No cluster multicast is used anywhere.
 //
-// Every wait is bounded: after kWaitLimit polls the waiter records a time-out in the
-// device status word and carries on (see wait_parity), so a protocol error can never hang
-// the GPU.
+// Every wait is bounded in TIME: a waiter that has seen kWaitLimitNs nanoseconds of the
+// GPU's global timer go by records a time-out in the device status word and carries on
+// (see wait_parity), so a protocol error can never hang the GPU.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -19,8 +19,14 @@ namespace tma {
 // reads and clears it through msd_device_status().
 int *device_status_ptr(int device);  // host; nullptr on failure
 
-constexpr uint32_t kWaitLimit = 1u << 24;      // polls of try_wait (each waits up to ~ms internally)
-constexpr uint32_t kAbortWaitLimit = 1u << 10; // once a time-out happened, later waits give up quickly
+constexpr uint64_t kWaitLimitNs = 4000000000ull;  // 4 s: far beyond any legitimate wait (a layer's kernel runs for milliseconds)
+constexpr uint64_t kAbortWaitLimitNs = 200000ull;  // once a time-out happened in the block, later waits give up after 0.2 ms
+
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -58,12 +64,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // Bounded wait for the phase with the given parity.  `abort_flag` is a shared-memory word
 // of the block: once any thread's wait ran out, all later waits in the block use the short
 // limit, the block keeps its control flow (so every barrier is still reached) and skips its
-// global stores; the host sees the code in the device status word.
-__device__ __forceinline__ void wait_parity(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
-    uint32_t limit = *abort_flag ? kAbortWaitLimit : kWaitLimit;
-    for (uint32_t i = 0; i < limit; ++i) {
+// global stores; the host sees the code in the device status word.  The limit is wall time
+// on the GPU's nanosecond timer, read only after a first batch of polls has failed.
+__device__ __forceinline__ void wait_parity(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int code,
+                                            uint64_t limit_ns = kWaitLimitNs) {
+#pragma unroll 1
+    for (int i = 0; i < 16; ++i)
         if (mbar_try_wait(bar, parity)) return;
-        if ((i & 1023u) == 1023u && *abort_flag) limit = kAbortWaitLimit;
+    const uint64_t t0 = globaltimer_ns();
+#pragma unroll 1
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (mbar_try_wait(bar, parity)) return;
+        const uint64_t limit = *abort_flag ? kAbortWaitLimitNs : limit_ns;
+        if (globaltimer_ns() - t0 > limit) break;
     }
     *abort_flag = 1;
     atomicCAS(status, 0, code);
@@ -105,10 +120,25 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
 // predecessor's tail; nothing the predecessor wrote may be touched before it.
 // allow_dependents() tells the scheduler that the NEXT kernel's blocks may be placed as soon
 // as resources free up.  Both are no-ops for kernels launched the ordinary way.
+//
+// The kernels stage their layer's WEIGHTS before the wait, so the attribute is only safe when
+// the predecessor in the stream is known not to write them.  The library therefore asks for it
+// only between the layer kernels of one msd_block_forward / msd_block_backward call (whose
+// first kernel is launched the ordinary way, i.e. after everything enqueued before the call
+// has completed); single-op and slab entry points always launch the ordinary way, so a weight
+// tensor produced by the kernel just before them (an initialiser, an optimiser step) is seen.
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void allow_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// Host: launch `kernel` on `s` with programmatic stream serialisation.
+// Host, per calling thread: may the next launches overlap their predecessor's tail?
+bool overlap_allowed();
+void set_overlap_allowed(bool on);
+struct OverlapScope {  // off on entry and on exit; the block entry points switch it on after their first launch
+    OverlapScope() { set_overlap_allowed(false); }
+    ~OverlapScope() { set_overlap_allowed(false); }
+};
+
+// Host: launch `kernel` on `s`, with programmatic stream serialisation when the calling thread allows it.
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args &&...args) {
     cudaLaunchConfig_t cfg = {};
@@ -120,7 +150,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = overlap_allowed() ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 

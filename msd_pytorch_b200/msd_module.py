@@ -70,6 +70,11 @@ class MSDModuleFunction(torch.autograd.Function):
     def forward(ctx, input, dilations, bias, final_weight, final_bias, *weights):
         depth = len(dilations)
         assert depth == len(weights), "number of weights does not match depth"
+        for i, w in enumerate(weights):
+            if w.dtype != input.dtype or bias.dtype != input.dtype or final_weight.dtype != input.dtype or final_bias.dtype != input.dtype:
+                raise RuntimeError("MSDModule: expected all tensors to have the same scalar type")
+            if not w.is_contiguous():
+                raise RuntimeError("MSDModule: expected weight%d to be contiguous" % i)
         c_in = input.shape[1]
         c_total = c_in + sum(w.shape[0] for w in weights)
         c_out = final_weight.shape[0]
@@ -92,6 +97,9 @@ class MSDModuleFunction(torch.autograd.Function):
         dev = result.device
         c_out, c_total = final_weight.shape[0], result.shape[1]
         grad_out = grad_out.contiguous()
+        if grad_out.data_ptr() % 16:
+            # a dense view that starts off a 16-byte boundary: the fused kernel reads 128-bit vectors
+            grad_out = grad_out.clone(memory_format=torch.contiguous_format)
         gradients = torch.empty_like(result)
         fw = final_weight.detach().reshape(c_out, c_total).contiguous()
         gfw = torch.zeros_like(fw)

@@ -14,6 +14,9 @@ OP_CASES = [
     ("3d_small", 1, 2, 2, (5, 6, 7), 2),
     ("3d_aligned", 1, 2, 2, (8, 8, 16), 2),
     ("3d_size_eq_dilation", 1, 1, 1, (3, 3, 4), 3),
+    ("2d_dilation10", 1, 3, 1, (12, 24), 10),
+    ("3d_dilation10", 1, 2, 1, (10, 11, 16), 10),
+    ("3d_ragged_size_eq_dilation", 2, 2, 2, (5, 7, 9), 5),
 ]
 
 # name, batch, c_in, depth, width, spatial, dilations
@@ -22,6 +25,8 @@ BLOCK_CASES = [
     ("block2d_w2", 1, 2, 3, 2, (9, 8), [1, 2, 4]),
     ("block3d", 1, 1, 4, 1, (8, 8, 16), [1, 2, 3, 1]),
     ("block3d_ragged", 1, 1, 3, 1, (5, 7, 9), [1, 2, 3]),
+    ("deep_block2d", 1, 1, 14, 1, (12, 20), [1 + (i % 10) for i in range(14)]),
+    ("deep_block3d", 1, 1, 12, 1, (10, 11, 12), [1 + (i % 10) for i in range(12)]),
 ]
 
 

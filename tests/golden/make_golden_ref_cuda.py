@@ -4,8 +4,8 @@ Needs a GPU and ``oracle/_ref/msd_custom_convolutions_ref.so`` (the reference's 
 native sources compiled unmodified by ``oracle/build_ref.py``).  The reference's op
 sequence for the dense block (msd_pytorch/msd_block.py:40-58,88-130) is replayed
 on top of its ops.  Output: ``<outdir>/ref_cuda_ops.npz`` and ``ref_cuda_block.npz``
-(float64 computations by the reference's double instantiations, plus float32 forward
-outputs), which are then committed under ``tests/golden/``.
+(float64 computations by the reference's double instantiations, plus the same from its
+float32 instantiations under ``*_f32_*`` keys), which are then committed under ``tests/golden/``.
 
 Usage (on a machine with a GPU):  python tests/golden/make_golden_ref_cuda.py <outdir>
 """
@@ -67,29 +67,29 @@ def main(outdir):
         a = cases.block_inputs(case)
         nd = len(sp)
         bs = blocks(nd)
-        dt = torch.float64
-        x = torch.from_numpy(a["x"]).to(dev, dt)
-        ws = [torch.from_numpy(w).to(dev, dt) for w in a["weights"]]
-        bias = torch.from_numpy(a["bias"]).to(dev, dt)
-        res = x.new_empty((B, c_in + depth * width) + tuple(sp))
-        res[:, :c_in] = x
-        for i in range(depth):
-            n = c_in + i * width
-            cc.conv_relu_forward(res[:, :n], ws[i], bias[i * width:(i + 1) * width], res[:, n:n + width], dil[i], block_size=bs)
-        grads = torch.from_numpy(a["gout"]).to(dev, dt).clone()
-        gb = torch.zeros_like(bias)
-        for i in range(depth - 1, -1, -1):
-            n = c_in + i * width
-            so, sg = res[:, n:n + width], grads[:, n:n + width]
-            cc.conv_relu_backward_x(so, sg, ws[i], grads[:, :n], dil[i], block_size=bs)
-            gw = torch.zeros_like(ws[i])
-            cc.conv_relu_backward_k(so, sg, res[:, :n], gw, dil[i], block_size=bs)
-            cc.conv_relu_backward_bias(so, sg, gb[i * width:(i + 1) * width], block_size=bs)
-            out[name + "_gw%d" % i] = gw.cpu().numpy()
-        torch.cuda.synchronize()
-        out[name + "_result"] = res.cpu().numpy()
-        out[name + "_gi"] = grads[:, :c_in].cpu().numpy()
-        out[name + "_gb"] = gb.cpu().numpy()
+        for dt, dtag in ((torch.float64, ""), (torch.float32, "_f32")):
+            x = torch.from_numpy(a["x"]).to(dev, dt)
+            ws = [torch.from_numpy(w).to(dev, dt) for w in a["weights"]]
+            bias = torch.from_numpy(a["bias"]).to(dev, dt)
+            res = x.new_empty((B, c_in + depth * width) + tuple(sp))
+            res[:, :c_in] = x
+            for i in range(depth):
+                n = c_in + i * width
+                cc.conv_relu_forward(res[:, :n], ws[i], bias[i * width:(i + 1) * width], res[:, n:n + width], dil[i], block_size=bs)
+            grads = torch.from_numpy(a["gout"]).to(dev, dt).clone()
+            gb = torch.zeros_like(bias)
+            for i in range(depth - 1, -1, -1):
+                n = c_in + i * width
+                so, sg = res[:, n:n + width], grads[:, n:n + width]
+                cc.conv_relu_backward_x(so, sg, ws[i], grads[:, :n], dil[i], block_size=bs)
+                gw = torch.zeros_like(ws[i])
+                cc.conv_relu_backward_k(so, sg, res[:, :n], gw, dil[i], block_size=bs)
+                cc.conv_relu_backward_bias(so, sg, gb[i * width:(i + 1) * width], block_size=bs)
+                out[name + dtag + "_gw%d" % i] = gw.cpu().numpy()
+            torch.cuda.synchronize()
+            out[name + dtag + "_result"] = res.cpu().numpy()
+            out[name + dtag + "_gi"] = grads[:, :c_in].cpu().numpy()
+            out[name + dtag + "_gb"] = gb.cpu().numpy()
     np.savez_compressed(os.path.join(outdir, "ref_cuda_block.npz"), **out)
     print("written to", outdir)
 

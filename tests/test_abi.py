@@ -87,3 +87,21 @@ def test_c_abi_argument_errors_need_no_gpu():
     dil = (ctypes.c_int * 2)(1, 1)
     assert L.msd_block_forward(0, _desc((1, 4, 4, 4)), 1, 2, 1, ptrs, 256, dil, None, 0, 0, None) == 1
     assert L.msd_workspace_bytes(0, 4, 1 << 20, 100, 1) > 0
+
+
+def test_noalloc_limit_boundaries_need_no_gpu():
+    """The built-in scratch of msd_conv_relu_backward_k_noalloc holds the partial sums of up to
+    356 input channels in 2D and 118 in 3D (one output channel); one more is refused with
+    MSD_ERR_LIMIT before anything touches a GPU."""
+    from msd_pytorch_b200 import _lib
+
+    L = _lib.lib
+    for shape, c_ok in (((1, 1, 16, 16), 356), ((1, 1, 8, 16, 16), 118)):
+        nd = len(shape)
+        assert L.msd_workspace_bytes(0, nd, 1 << 20, c_ok, 1) <= L.msd_noalloc_scratch_bytes() < L.msd_workspace_bytes(0, nd, 1 << 20, c_ok + 1, 1)
+        y = _desc(shape)
+        x = _desc((1, c_ok + 1) + shape[2:])
+        assert L.msd_conv_relu_backward_k_noalloc(0, y, y, x, 256, 1, 0, None) == 5
+        assert b"built-in array" in L.msd_last_error_string()
+        x = _desc((1, c_ok) + shape[2:])
+        assert L.msd_conv_relu_backward_k_noalloc(0, y, y, x, 256, 1, 0, None) != 5  # accepted as far as the limit goes (no GPU here)

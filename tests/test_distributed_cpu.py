@@ -46,6 +46,13 @@ def _bucket_case(rank, world, out_dir):
     mean = sum(range(1, world + 1)) / world
     for k, p in enumerate(params):
         assert torch.allclose(p.grad, torch.full_like(p, mean * (k + 1)))
+    # the gradients now ARE slices of the flat buffer: accumulating in place and reducing again needs no gather
+    for k, p in enumerate(params):
+        assert p.grad.data_ptr() == bucket.views[k].data_ptr()
+        p.grad.fill_(float(rank + 1))
+    bucket.allreduce_(average=False)
+    for p in params:
+        assert torch.allclose(p.grad, torch.full_like(p, float(sum(range(1, world + 1)))))
     assert split_batch(16, rank, world) == (rank * 16 // world, (rank + 1) * 16 // world)
     with pytest.raises(ValueError):
         split_batch(3, rank, 2)
@@ -64,6 +71,67 @@ def _halo_case(rank, world, out_dir):
     first_global = loc["g0"] - loc["lo"]
     for k in range(loc["planes"]):
         assert torch.all(vol[k] == float(first_global + k)), (rank, k, vol[k, 0, 0].item())
+
+
+def _partial_sum_case(rank, world, out_dir):
+    """The forward's hand-over of z-tap partial sums and the backward's of gradient planes,
+    started asynchronously like the slab schedule does, on CPU tensors."""
+    from msd_pytorch_b200.distributed import SlabPlan, TorchRanks, halo_transfers, partial_sum_transfers
+
+    Z, H, d = 24, 5, 3
+    plan = SlabPlan(Z, world, H)
+    loc = plan.local(rank)
+    comm = TorchRanks()
+    # u[tap][z] = 100 * tap + global plane index on the owned planes, -1 elsewhere
+    u = torch.full((3, loc["planes"], 2, 2), -1.0)
+    for tap in range(3):
+        for z in range(loc["g0"], loc["g1"]):
+            u[tap, loc["z_begin"] + z - loc["g0"]] = 100.0 * tap + z
+    work = comm.start({rank: [(k, peer, tap, u[tap, a:b]) for k, peer, tap, a, b in partial_sum_transfers(plan, rank, d)]})
+    work.wait()
+    zb, ze = loc["z_begin"], loc["z_end"]
+    if rank > 0:       # u_0 of the d planes below my first owned one
+        for j in range(d):
+            assert torch.all(u[0, zb - d + j] == float(loc["g0"] - d + j))
+        assert torch.all(u[2, zb - 1] == -1.0) and torch.all(u[1, zb - 1] == -1.0)
+    if rank < world - 1:  # u_2 of the d planes above my last owned one
+        for j in range(d):
+            assert torch.all(u[2, ze + j] == 200.0 + loc["g1"] + j)
+        assert torch.all(u[0, ze] == -1.0)
+    # gradient channel: only d planes per face travel
+    g = torch.full((loc["planes"], 2, 2), -1.0)
+    g[zb:ze] = torch.arange(loc["g0"], loc["g1"], dtype=torch.float32).view(-1, 1, 1).expand(-1, 2, 2)
+    comm.start({rank: [(k, peer, 0, g[a:b]) for k, peer, a, b in halo_transfers(plan, rank, d)]}).wait()
+    first = loc["g0"] - loc["lo"]
+    for k in range(loc["planes"]):
+        inside = (zb - (d if rank > 0 else 0)) <= k < (ze + (d if rank < world - 1 else 0))
+        assert torch.all(g[k] == (float(first + k) if inside else -1.0)), (rank, k)
+
+
+def test_partial_sum_and_gradient_handover_gloo(tmp_path):
+    _run("_partial_sum_case", 3, tmp_path)
+
+
+def test_boundary_windows_and_partial_sum_schedule():
+    from msd_pytorch_b200.distributed import SlabPlan, VirtualRanks, boundary_windows, partial_sum_transfers
+
+    plan = SlabPlan(60, 3, 10)
+    assert boundary_windows(plan, 0, 4) == ([(16, 20)], [(0, 16)])
+    assert boundary_windows(plan, 1, 4) == ([(10, 14), (26, 30)], [(14, 26)])
+    assert boundary_windows(plan, 2, 10) == ([(10, 20)], [(20, 30)])
+    assert boundary_windows(SlabPlan(60, 1, 0), 0, 7) == ([], [(0, 60)])
+    assert boundary_windows(SlabPlan(36, 3, 10), 1, 6) == ([(10, 22)], [])   # 12 planes cannot be split 6 + interior + 6
+    assert partial_sum_transfers(plan, 1, 3) == [("send", 0, 2, 10, 13), ("recv", 0, 0, 7, 10), ("send", 2, 0, 27, 30), ("recv", 2, 2, 30, 33)]
+    with pytest.raises(ValueError):
+        partial_sum_transfers(plan, 1, 11)
+    # every send has exactly one matching receive of the same size
+    bufs = {r: torch.zeros(3, plan.local(r)["planes"]) for r in range(3)}
+    for r in range(3):
+        loc = plan.local(r)
+        bufs[r][:, loc["z_begin"]:loc["z_end"]] = torch.arange(loc["g0"], loc["g1"], dtype=torch.float32) + 1000.0 * torch.arange(3).view(3, 1)
+    VirtualRanks(3).start({r: [(k, p, tap, bufs[r][tap, a:b]) for k, p, tap, a, b in partial_sum_transfers(plan, r, 3)] for r in range(3)})
+    assert bufs[1][0, 7:10].tolist() == [17.0, 18.0, 19.0] and bufs[1][2, 30:33].tolist() == [2040.0, 2041.0, 2042.0]
+    assert bufs[0][2, 20:23].tolist() == [2020.0, 2021.0, 2022.0] and bufs[2][0, 7:10].tolist() == [37.0, 38.0, 39.0]
 
 
 def test_gradient_bucket_allreduce_gloo(tmp_path):

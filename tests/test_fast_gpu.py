@@ -233,3 +233,73 @@ def test_backward3d_role_split_variant(cuda_device, sp, B, depth):
     finally:
         for d in range(1, 11):
             _lib.lib.msd_tuning_set(_lib.FAMILY_BWD3D, d, -1)
+
+
+@pytest.mark.parametrize("sp", [(12, 22, 128), (11, 18, 256)], ids=["x128", "x256"])
+def test_role_split_3d_backward_against_cpu_oracle(cuda_device, sp):
+    """The role-split 3D backward kernel (X warps + K warps, used for X % 128 == 0) directly
+    against the float64 CPU oracle: a depth-22 block with ragged Z and Y so that every
+    dilation 1..10 runs with at least 12 input channels, the split variant forced, and the
+    number of its launches asserted."""
+    from oracle import msd_oracle as O
+    from msd_pytorch_b200 import _lib
+    from msd_pytorch_b200.msd_block import msd_block
+
+    dev = cuda_device
+    L = _lib.lib
+    depth = 22
+    dil = [1 + (i % 10) for i in range(depth)]
+    g = torch.Generator().manual_seed(515)
+    x = torch.randn(1, 1, *sp, generator=g)
+    ws = [torch.randn(1, 1 + i, 3, 3, 3, generator=g) * (2.0 / (27 * (1 + i))) ** 0.5 for i in range(depth)]
+    bias = 0.05 * torch.randn(depth, generator=g)
+    gout = torch.randn(1, 1 + depth, *sp, generator=g)
+    res_o = O.msd_block_forward(x.double(), dil, bias.double(), [w.double() for w in ws])
+    old = [L.msd_tuning_get(_lib.FAMILY_BWD3D, d) for d in range(1, 11)]
+    try:
+        for d in range(1, 11):
+            assert L.msd_tuning_set(_lib.FAMILY_BWD3D, d, 1) == 0
+        split0 = L.msd_split_launch_count()
+        xd = x.to(dev).requires_grad_(True)
+        wd = [w.to(dev).requires_grad_(True) for w in ws]
+        bd = bias.to(dev).requires_grad_(True)
+        res = msd_block(xd, dil, bd, *wd)
+        res.backward(gout.to(dev))
+        torch.cuda.synchronize()
+        # layers with >= 8 input channels (dilation <= 5) or >= 12 (above) take the split kernel
+        expect = sum(1 for i in range(depth) if 1 + i >= (8 if dil[i] <= 5 else 12))
+        assert L.msd_split_launch_count() - split0 == expect
+        assert _lib.device_status(dev) == 0
+    finally:
+        for d, v in zip(range(1, 11), old):
+            L.msd_tuning_set(_lib.FAMILY_BWD3D, d, v)
+    assert_close(res.detach(), res_o, 1e-4, "activations")
+    gi_o, gb_o, gws_o = O.msd_block_backward(res.detach().double().cpu(), gout.double(), dil, bias.double(), [w.double() for w in ws])
+    assert_close(xd.grad, gi_o, 1e-3, "grad_input")
+    assert_close(bd.grad, gb_o, 1e-3, "grad_bias")
+    for i, (w, e) in enumerate(zip(wd, gws_o)):
+        assert_close(w.grad, e, 1e-3, "grad_weight%d" % i)
+
+
+def test_bounded_wait_runs_out_and_reports(cuda_device):
+    """A wait on a barrier nobody arrives at gives up after its time limit: the kernel returns
+    by itself, the device status word carries the code, reading it clears it, and the next
+    ordinary call works."""
+    import time
+    from msd_pytorch_b200 import _lib
+    from msd_pytorch_b200 import msd_custom_convolutions as cc
+
+    dev = cuda_device
+    L = _lib.lib
+    assert _lib.device_status(dev) == 0
+    t0 = time.time()
+    assert L.msd_selftest_wait_timeout(1_000_000, dev.index, _lib.stream_of(dev)) == 0  # 1 ms
+    assert _lib.device_status(dev) == 99  # MSD_STATUS_SELFTEST_TIMEOUT; synchronises the stream
+    assert time.time() - t0 < 5.0, "the wait must end after about a millisecond"
+    assert _lib.device_status(dev) == 0, "reading the status clears it"
+    assert L.msd_selftest_wait_timeout(10, dev.index, _lib.stream_of(dev)) == 1  # limit outside [1e3, 1e9]
+    x = torch.randn(1, 2, 32, 64, device=dev)
+    y = torch.empty(1, 1, 32, 64, device=dev)
+    cc.conv_relu_forward(x, torch.randn(1, 2, 3, 3, device=dev), torch.zeros(1, device=dev), y, 2)
+    torch.cuda.synchronize()
+    assert torch.isfinite(y).all() and _lib.device_status(dev) == 0
