@@ -57,17 +57,31 @@ def _final_kernels_apply(result, c_out):
     return result.is_cuda and result.dtype == torch.float32 and c_out <= 8 and result.shape[-1] % 4 == 0 and result.is_contiguous()
 
 
-class MSDModuleFunction(torch.autograd.Function):
-    """Dense block + final 1x1 layer as ONE autograd node.
+def _scale_parts(conv):
+    """(weight [c, c], bias [c]) of a 1x1(x1) convolution module used as a normalisation layer."""
+    c = conv.weight.shape[0]
+    return conv.weight.detach().reshape(c, c), conv.bias.detach()
 
-    Same arithmetic as ``MSDFinalLayer(msd_block(input, ...))`` (msd_module.py:144-147 of the
-    reference).  What the fusion removes is data movement: the final layer's backward writes
-    the gradient of every channel straight into the buffer that the block backward updates
-    in place, so the dense gradient tensor that autograd would pass between the two nodes,
-    and the copy of it that the block backward must take (msd_block.py:83), never exist."""
+
+class MSDModuleFunction(torch.autograd.Function):
+    """Dense block + final 1x1 layer as ONE autograd node, optionally with the model's frozen
+    normalisation layers folded in.
+
+    Same arithmetic as ``scale_out(MSDFinalLayer(msd_block(scale_in(input), ...)))``
+    (msd_module.py:144-147 and msd_model.py:8-45 of the reference).  What the fusion removes is
+    data movement: the final layer's backward writes the gradient of every channel straight
+    into the buffer that the block backward updates in place, so the dense gradient tensor that
+    autograd would pass between the two nodes, and the copy of it that the block backward must
+    take (msd_block.py:83), never exist.  The input normalisation happens in the copy that
+    places the input into the channel buffer (one pass instead of two); the output
+    normalisation is a c_out x c_out matrix applied to the final layer's WEIGHTS, so that the
+    final layer's store already writes normalised values and no pass over the output is left.
+
+    ``scales`` is ``(w_in [c_in, c_in], b_in [c_in], w_out [c_out, c_out], b_out [c_out])`` or
+    None; the four are treated as constants (they are frozen in the models)."""
 
     @staticmethod
-    def forward(ctx, input, dilations, bias, final_weight, final_bias, *weights):
+    def forward(ctx, input, dilations, bias, final_weight, final_bias, scales, *weights):
         depth = len(dilations)
         assert depth == len(weights), "number of weights does not match depth"
         for i, w in enumerate(weights):
@@ -79,45 +93,73 @@ class MSDModuleFunction(torch.autograd.Function):
         c_total = c_in + sum(w.shape[0] for w in weights)
         c_out = final_weight.shape[0]
         result = input.new_empty(input.shape[0], c_total, *input.shape[2:])
-        result[:, :c_in] = input
+        fw = final_weight.detach().reshape(c_out, c_total)
+        fb = final_bias.detach()
+        ones = (1,) * (input.dim() - 2)
+        if scales is None:
+            result[:, :c_in] = input
+            w_out = None
+        else:
+            w_in, b_in, w_out, b_out = scales
+            if c_in == 1:
+                torch.addcmul(b_in.view(1, 1, *ones), input, w_in.view(1, 1, *ones), out=result[:, :1])
+            else:
+                result[:, :c_in] = (torch.matmul(w_in, input.flatten(2)) + b_in.view(1, c_in, 1)).view_as(input)
+            if w_out is not None:
+                fb = torch.mv(w_out, fb) + b_out if c_out > 1 else fb * w_out.view(()) + b_out
+                fw = torch.matmul(w_out, fw) if c_out > 1 else fw * w_out.view(())
         block_forward_(result, c_in, list(dilations), bias.contiguous(), [w.detach() for w in weights])
         out = input.new_empty(input.shape[0], c_out, *input.shape[2:])
         dev = input.device
-        fw = final_weight.detach().reshape(c_out, c_total).contiguous()
-        _lib.check(_lib.lib.msd_final_forward(_lib.MSD_F32, _lib.describe(result), fw.data_ptr(), final_bias.detach().contiguous().data_ptr(),
+        fw = fw.contiguous()
+        _lib.check(_lib.lib.msd_final_forward(_lib.MSD_F32, _lib.describe(result), fw.data_ptr(), fb.contiguous().data_ptr(),
                                               _lib.describe(out), dev.index, _lib.stream_of(dev)))
         ctx.dilations = list(dilations)
         ctx.c_in = c_in
-        ctx.save_for_backward(bias, result, final_weight, *weights)
+        ctx.w_in = None if scales is None else scales[0]
+        ctx.w_out = w_out
+        ctx.save_for_backward(bias, result, fw, final_weight, *weights)
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
-        bias, result, final_weight, *weights = ctx.saved_tensors
+        bias, result, fw, final_weight, *weights = ctx.saved_tensors
         dev = result.device
-        c_out, c_total = final_weight.shape[0], result.shape[1]
+        c_out, c_total = fw.shape[0], result.shape[1]
         grad_out = grad_out.contiguous()
         if grad_out.data_ptr() % 16:
             # a dense view that starts off a 16-byte boundary: the fused kernel reads 128-bit vectors
             grad_out = grad_out.clone(memory_format=torch.contiguous_format)
         gradients = torch.empty_like(result)
-        fw = final_weight.detach().reshape(c_out, c_total).contiguous()
         gfw = torch.zeros_like(fw)
         gfb = torch.zeros(c_out, dtype=result.dtype, device=dev)
         ws = _lib.workspace(dev, _lib.lib.msd_final_workspace_bytes(c_total, c_out))
         _lib.check(_lib.lib.msd_final_backward(_lib.MSD_F32, _lib.describe(result), _lib.describe(grad_out), fw.data_ptr(), _lib.describe(gradients),
                                                gfw.data_ptr(), gfb.data_ptr(), ws.data_ptr(), ws.numel(), dev.index, _lib.stream_of(dev)))
+        if ctx.w_out is not None:
+            # fw = w_out @ final_weight: gradients with respect to the layer's own parameters
+            if c_out > 1:
+                gfw, gfb = torch.matmul(ctx.w_out.t(), gfw), torch.mv(ctx.w_out.t(), gfb)
+            else:
+                gfw, gfb = gfw * ctx.w_out.view(()), gfb * ctx.w_out.view(())
         # one zero-filled buffer for all weight gradients (a single fill instead of one per layer)
         sizes = [w.numel() for w in weights]
         flat = torch.zeros(sum(sizes), dtype=result.dtype, device=dev)
         grad_weights, off = [], 0
         for w, n in zip(weights, sizes):
-            grad_weights.append(flat[off:off + n].view_as(w) if ctx.needs_input_grad[5 + len(grad_weights)] else None)
+            grad_weights.append(flat[off:off + n].view_as(w) if ctx.needs_input_grad[6 + len(grad_weights)] else None)
             off += n
         grad_bias = torch.zeros_like(bias) if ctx.needs_input_grad[2] else None
         block_backward_(result, gradients, ctx.c_in, ctx.dilations, [w.detach() for w in weights], grad_weights, grad_bias)
-        grad_input = gradients[:, :ctx.c_in] if ctx.needs_input_grad[0] else None
-        return (grad_input, None, grad_bias, gfw.view_as(final_weight), gfb, *grad_weights)
+        grad_input = None
+        if ctx.needs_input_grad[0]:
+            grad_input = gradients[:, :ctx.c_in]
+            if ctx.w_in is not None:
+                if ctx.c_in == 1:
+                    grad_input = grad_input * ctx.w_in.view(())
+                else:
+                    grad_input = torch.matmul(ctx.w_in.t(), grad_input.flatten(2)).view(grad_input.shape)
+        return (grad_input, None, grad_bias, gfw.view_as(final_weight), gfb, None, *grad_weights)
 
 
 class MSDModule(torch.nn.Module):
@@ -145,10 +187,27 @@ class MSDModule(torch.nn.Module):
         self.msd_block.bias.data.zero_()
         self.final_layer.reset_parameters()
 
+    def _fused_applies(self, input):
+        return input.dim() in (4, 5) and _final_kernels_apply(input, self.c_out) and input.shape[-1] * 4 % 16 == 0
+
     def forward(self, input):
+        return self.forward_scaled(input, None, None)
+
+    def forward_scaled(self, input, scale_in=None, scale_out=None):
+        """``scale_out(self(scale_in(input)))`` for frozen 1x1 normalisation layers (either may
+        be None).  On the fused path the two layers cost no pass over the data of their own."""
         blk = self.msd_block
-        if input.dim() in (4, 5) and _final_kernels_apply(input, self.c_out) and input.shape[-1] * 4 % 16 == 0:
+        frozen = all(not p.requires_grad for m in (scale_in, scale_out) if m is not None for p in m.parameters())
+        if self._fused_applies(input) and frozen:
             weights = (getattr(blk, "weight{}".format(i)) for i in range(len(blk.weights)))
+            scales = None
+            if scale_in is not None or scale_out is not None:
+                dev, dt = input.device, input.dtype
+                w_in, b_in = _scale_parts(scale_in) if scale_in is not None else (torch.eye(self.c_in, device=dev, dtype=dt), torch.zeros(self.c_in, device=dev, dtype=dt))
+                w_out, b_out = _scale_parts(scale_out) if scale_out is not None else (None, None)
+                scales = (w_in, b_in, w_out, b_out)
             return MSDModuleFunction.apply(input.contiguous(), blk.dilations, blk.bias, self.final_layer.linear.weight,
-                                           self.final_layer.linear.bias, *weights)
-        return self.final_layer(blk(input))
+                                           self.final_layer.linear.bias, scales, *weights)
+        x = input if scale_in is None else scale_in(input)
+        y = self.final_layer(blk(x))
+        return y if scale_out is None else scale_out(y)

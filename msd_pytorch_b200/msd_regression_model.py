@@ -1,7 +1,7 @@
 """MSD network for regression (API of the reference's msd_pytorch/msd_regression_model.py:8-82)."""
 import torch.nn as nn
 
-from .msd_model import MSDModel
+from .msd_model import MSDModel, NormalizedNet
 from .msd_module import DEFAULT_DILATIONS
 
 loss_functions = {"L1": nn.L1Loss(), "L2": nn.MSELoss()}
@@ -13,7 +13,7 @@ class MSDRegressionModel(MSDModel):
         self.criterion = loss_functions.get(loss)
         if self.criterion is None:
             raise ValueError(f"The loss must be one of {list(loss_functions.keys())}. Supplied {loss}. ")
-        self.net = nn.Sequential(self.scale_in, self.msd, self.scale_out)
+        self.net = NormalizedNet(self.scale_in, self.msd, self.scale_out)
         self.net.cuda()
         if parallel:
             self.net = nn.DataParallel(self.net)

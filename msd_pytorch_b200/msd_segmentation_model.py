@@ -2,7 +2,7 @@
 import numpy as np
 import torch.nn as nn
 
-from .msd_model import MSDModel, scaling_module_set_bias, scaling_module_set_scale
+from .msd_model import MSDModel, NormalizedNet, scaling_module_set_bias, scaling_module_set_scale
 from .msd_module import DEFAULT_DILATIONS
 
 
@@ -12,7 +12,7 @@ class MSDSegmentationModel(MSDModel):
         super().__init__(c_in, num_labels, depth, width, dilations, ndim=ndim)
         self.criterion = nn.NLLLoss()
         net_trained = nn.Sequential(self.msd, nn.LogSoftmax(dim=1))
-        self.net = nn.Sequential(self.scale_in, net_trained)
+        self.net = NormalizedNet(self.scale_in, net_trained)
         self.net.cuda()
         if parallel:
             self.net = nn.DataParallel(self.net)

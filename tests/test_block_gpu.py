@@ -392,3 +392,40 @@ def test_weights_written_by_the_preceding_kernel_are_seen(cuda_device):
         y_o = torch.empty(2, 1, 128, 256, dtype=torch.float64)
         O.conv_relu_forward(x.double(), k_new.double(), b.double(), y_o, 3)
         assert_close(y, y_o, 1e-4, "forward after a weight write")
+
+
+@pytest.mark.parametrize("ndim,c_in,c_out,seg", [(2, 1, 1, False), (3, 1, 1, False), (2, 2, 3, False), (2, 1, 4, True)],
+                         ids=["2d_1to1", "3d_1to1", "2d_2to3", "segmentation"])
+def test_normalisation_layers_folded_into_the_module(cuda_device, ndim, c_in, c_out, seg):
+    """model.net (normalisation folded into the block's first load and the final layer's
+    store) against the plain composition scale_out(msd(scale_in(x))) of the same modules:
+    outputs, parameter gradients and the input gradient; state-dict keys as in the reference."""
+    from msd_pytorch_b200 import MSDRegressionModel, MSDSegmentationModel
+
+    torch.manual_seed(11)
+    dev = cuda_device
+    sp = (24, 32) if ndim == 2 else (8, 12, 16)
+    model = (MSDSegmentationModel(c_in, c_out, 5, 1, ndim=ndim) if seg else MSDRegressionModel(c_in, c_out, 5, 1, ndim=ndim))
+    for p in model.msd.parameters():
+        p.data.normal_(0, 0.3)
+    for sm in (model.scale_in,) + (() if seg else (model.scale_out,)):
+        sm.weight.data.normal_(0, 1.0)     # a full matrix, not only a diagonal
+        sm.bias.data.normal_(0, 1.0)
+    keys = list(model.net.state_dict().keys())
+    assert keys[0] == "0.weight" and ("1.0.msd_block.bias" if seg else "1.msd_block.bias") in keys
+    x = torch.randn(2, c_in, *sp, device=dev)
+    x1 = x.clone().requires_grad_(True)
+    out = model.net(x1)
+    out.square().sum().backward()
+    got = [p.grad.clone() for p in model.msd.parameters()]
+    for p in model.msd.parameters():
+        p.grad = None
+    x2 = x.clone().requires_grad_(True)
+    y = model.msd(model.scale_in(x2))
+    y = torch.log_softmax(y, dim=1) if seg else model.scale_out(y)
+    y.square().sum().backward()
+    assert_close(out, y, 1e-5, "output")
+    assert_close(x1.grad, x2.grad, 1e-4, "grad_input")
+    for a, p in zip(got, model.msd.parameters()):
+        assert_close(a, p.grad, 1e-4, "parameter gradient")
+    assert all(p.grad is None for p in model.scale_in.parameters())
