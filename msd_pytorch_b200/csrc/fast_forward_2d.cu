@@ -132,12 +132,16 @@ static const Fwd2dVariant kFwd2d[10][kNumFwd2dVariants] = {
 };
 // 3D (three z-taps per staged plane), per dilation: variant 0 = 4-row lattice, 4 column
 // segments per thread; variant 1 = 4-row lattice, 2 segments (twice the warps, shorter tiles
-// where the block would otherwise exceed ~500 threads and run out of registers).
-static const Fwd2dVariant kFwd3d[10][2] = {
-    {V(1, 4, 8, 4, 3, 128), V(1, 4, 6, 2, 3, 128)}, {V(2, 4, 4, 4, 3, 128), V(2, 4, 3, 2, 3, 128)}, {V(3, 4, 3, 4, 3, 128), V(3, 4, 2, 2, 3, 128)},
-    {V(4, 4, 2, 4, 3, 128), V(4, 4, 1, 2, 3, 128)}, {V(5, 4, 2, 4, 3, 128), V(5, 4, 1, 2, 3, 128)}, {V(6, 4, 2, 4, 3, 128), V(6, 4, 1, 2, 3, 128)},
-    {V(7, 4, 2, 4, 3, 128), V(7, 4, 1, 2, 3, 128)}, {V(8, 4, 1, 4, 3, 128), V(8, 4, 1, 2, 3, 128)}, {V(9, 4, 1, 4, 3, 128), V(9, 4, 1, 2, 3, 128)},
-    {V(10, 4, 1, 4, 3, 128), V(10, 4, 1, 2, 3, 128)},
+// where the block would otherwise exceed ~500 threads and run out of registers); variant 2 =
+// variant 0 with more row stacks for the small dilations (12-13 compute warps instead of 8-9:
+// the kernel is bound by FP32 issue, and more resident warps hide its shared-memory latency).
+static const int kNumFwd3dVariants = 3;
+static const Fwd2dVariant kFwd3d[10][kNumFwd3dVariants] = {
+    {V(1, 4, 8, 4, 3, 128), V(1, 4, 6, 2, 3, 128), V(1, 4, 13, 4, 3, 128)}, {V(2, 4, 4, 4, 3, 128), V(2, 4, 3, 2, 3, 128), V(2, 4, 6, 4, 3, 128)},
+    {V(3, 4, 3, 4, 3, 128), V(3, 4, 2, 2, 3, 128), V(3, 4, 4, 4, 3, 128)},  {V(4, 4, 2, 4, 3, 128), V(4, 4, 1, 2, 3, 128), V(4, 4, 3, 4, 3, 128)},
+    {V(5, 4, 2, 4, 3, 128), V(5, 4, 1, 2, 3, 128), V(5, 4, 2, 4, 3, 128)},  {V(6, 4, 2, 4, 3, 128), V(6, 4, 1, 2, 3, 128), V(6, 4, 2, 4, 3, 128)},
+    {V(7, 4, 2, 4, 3, 128), V(7, 4, 1, 2, 3, 128), V(7, 4, 2, 4, 3, 128)},  {V(8, 4, 1, 4, 3, 128), V(8, 4, 1, 2, 3, 128), V(8, 4, 1, 4, 3, 128)},
+    {V(9, 4, 1, 4, 3, 128), V(9, 4, 1, 2, 3, 128), V(9, 4, 1, 4, 3, 128)},  {V(10, 4, 1, 4, 3, 128), V(10, 4, 1, 2, 3, 128), V(10, 4, 1, 4, 3, 128)},
 };
 #undef V
 
@@ -147,7 +151,7 @@ int num_variants(int family) {
     switch (family) {
         case FWD2D: return kNumFwd2dVariants;  // lattice rows x column segments x tile width
         case BWD2D: return 2;  // 4 / 8 voxels per thread
-        case FWD3D: return 2;  // 4 / 2 column segments per thread
+        case FWD3D: return kNumFwd3dVariants;  // 4 / 2 column segments per thread / more row stacks
         case BWD3D: return 2;  // unsplit consumers / X warps + K warps
         default: return 1;
     }
@@ -156,7 +160,7 @@ int num_variants(int family) {
 static bool fwd_plan(const View &in, int nd, int d, const Fwd2dVariant **var, int *stages) {
     if (d < 1 || d > 10) return false;
     const int wp = nd == 3 ? 28 : 12;
-    const int nvar = nd == 3 ? 2 : kNumFwd2dVariants;
+    const int nvar = nd == 3 ? kNumFwd3dVariants : kNumFwd2dVariants;
     int v = tuning_get(nd == 3 ? FWD3D : FWD2D, d);
     if (v < 0 || v >= nvar) v = 0;
     const Fwd2dVariant *cand = nd == 3 ? &kFwd3d[d - 1][v] : &kFwd2d[d - 1][v];

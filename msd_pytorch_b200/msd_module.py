@@ -37,12 +37,14 @@ class MSDFinalLayer(torch.nn.Module):
         self.reset_parameters()
 
     def forward(self, input):
-        # Same arithmetic as applying ``self.linear`` (a Conv1d with kernel size 1) to the
-        # flattened view, written as one matrix product per sample: the layer is a pure
-        # stream over the dense channel buffer and the GEMM path keeps it near copy speed,
-        # forward and backward.
         b, c_in, *size = input.shape
         flat = input.reshape(b, c_in, -1)
+        if input.dtype != torch.float32:
+            # exactly the reference's arithmetic: the Conv1d itself on the flattened view
+            return self.linear(flat).view(b, self.c_out, *size)
+        # float32: the same sum written as one matrix product per sample; the layer is a pure
+        # stream over the dense channel buffer and the GEMM path keeps it near copy speed,
+        # forward and backward.
         out = torch.matmul(self.linear.weight[:, :, 0], flat) + self.linear.bias[None, :, None]
         return out.view(b, self.c_out, *size)
 

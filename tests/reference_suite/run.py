@@ -89,14 +89,45 @@ def install(mode):
     return os.path.join(root, "msd_pytorch", "tests")
 
 
+class _Failures:
+    """pytest plugin: remembers the node ids that failed."""
+
+    def __init__(self):
+        self.failed = []
+
+    def pytest_runtest_logreport(self, report):
+        if report.failed and report.nodeid not in self.failed:
+            self.failed.append(report.nodeid)
+
+
 def run_tests(mode, extra):
+    """Runs the files; a test that fails is repeated up to two more times on its own and counts
+    as failed only if it fails every time.  (The reference's gradcheck tests draw UNSEEDED
+    random inputs and compare against finite differences with a step of 1e-6: now and then a
+    ReLU pre-activation lies within that step of zero and the numerical Jacobian is off.)"""
     import pytest
 
     tests = install(mode)
+    root = os.path.dirname(os.path.dirname(tests))
     files = [os.path.join(tests, f) for f in TEST_FILES]
     # rootdir = the checkout, so that the files import as msd_pytorch.tests.*; no cache files are
     # written into the (possibly read-only) checkout
-    return pytest.main(["-q", "-p", "no:cacheprovider", "--rootdir", os.path.dirname(os.path.dirname(tests)), "-W", "ignore"] + files + list(extra))
+    base = ["-q", "-p", "no:cacheprovider", "--rootdir", root, "-W", "ignore"]
+    seen = _Failures()
+    rc = pytest.main(base + files + list(extra), plugins=[seen])
+    if rc == 0 or not seen.failed or "--collect-only" in extra:
+        return rc
+    still = list(seen.failed)
+    for attempt in range(2):
+        again = _Failures()
+        os.chdir(root)
+        rc = pytest.main(base + still, plugins=[again])
+        still = again.failed
+        if not still:
+            print("reference suite: %d test(s) failed once and passed when repeated: %s" % (len(seen.failed), ", ".join(seen.failed)))
+            return 0
+    print("reference suite: failed three times in a row: %s" % ", ".join(still))
+    return 1
 
 
 def checkpoint_roundtrip(tmpdir):

@@ -429,3 +429,29 @@ def test_normalisation_layers_folded_into_the_module(cuda_device, ndim, c_in, c_
     for a, p in zip(got, model.msd.parameters()):
         assert_close(a, p.grad, 1e-4, "parameter gradient")
     assert all(p.grad is None for p in model.scale_in.parameters())
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_block_gradcheck_reference_configuration(cuda_device, seed):
+    """The configuration of the reference's own 2D block gradcheck (test_msd_block.py:27-46:
+    3 input channels, 13x21, dilations 1..3, width 1, float64), seeded, against the oracle
+    and against finite differences."""
+    from oracle import msd_oracle as O
+    from msd_pytorch_b200.msd_block import MSDBlock2d
+
+    torch.manual_seed(seed)
+    dev = cuda_device
+    net = MSDBlock2d(3, [1, 2, 3]).to(dev).double()
+    x = torch.randn(2, 3, 13, 21, dtype=torch.float64, device=dev, requires_grad=True)
+    res = net(x)
+    gout = torch.randn_like(res)
+    res.backward(gout)
+    ws = [getattr(net, "weight%d" % i).detach().cpu() for i in range(3)]
+    res_o = O.msd_block_forward(x.detach().cpu(), [1, 2, 3], net.bias.detach().cpu(), ws)
+    gi_o, gb_o, gws_o = O.msd_block_backward(res_o, gout.cpu(), [1, 2, 3], net.bias.detach().cpu(), ws)
+    assert_close(res.detach(), res_o, 1e-11, "result")
+    assert_close(x.grad, gi_o, 1e-10, "grad_input")
+    assert_close(net.bias.grad, gb_o, 1e-10, "grad_bias")
+    for i, e in enumerate(gws_o):
+        assert_close(getattr(net, "weight%d" % i).grad, e, 1e-10, "grad_weight%d" % i)
+    assert torch.autograd.gradcheck(net, (x.detach().clone().requires_grad_(True),), atol=1e-5, rtol=1e-3, nondet_tol=1e-9)
