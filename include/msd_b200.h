@@ -223,7 +223,9 @@ MSD_API int msd_slab_layer_backward(const msd_tensor_t *result, const msd_tensor
  * 3D backward: variant 0 = one kind of consumer warp computes both gradients,
  * variant 1 (default) = warps split by role (input-gradient warps, weight-gradient
  * warps, table builders) for layers with 8 (dilation <= 5) or 12 and more input
- * channels whose x extent is a multiple of 128. */
+ * channels whose x extent is a multiple of 128; variant 2 = both gradients as TF32
+ * tensor-core contractions with error-compensated operand splitting (tcgen05; 8 to
+ * 128 input channels, x extent a multiple of 128, already gated gradient). */
 MSD_API int msd_tuning_num_variants(int family);
 
 /* Force variant `variant` (or -1 = library default) for (family, dilation).
@@ -239,6 +241,7 @@ MSD_API int msd_tuning_get(int family, int dilation);
 MSD_API int64_t msd_launch_count(void);
 MSD_API int64_t msd_fast_launch_count(void);
 MSD_API int64_t msd_split_launch_count(void); /* of those, launches of the role-split 3D backward kernel */
+MSD_API int64_t msd_mma_launch_count(void);   /* of those, launches of the tensor-core 3D backward kernel */
 MSD_API void msd_reset_launch_count(void);
 
 /* No counterpart in the reference: msd_conv_relu_backward_k for callers that cannot

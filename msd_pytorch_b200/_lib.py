@@ -67,6 +67,7 @@ def _load():
         "msd_launch_count": (i64, []),
         "msd_fast_launch_count": (i64, []),
         "msd_split_launch_count": (i64, []),
+        "msd_mma_launch_count": (i64, []),
         "msd_reset_launch_count": (None, []),
         "msd_device_status": (i, [i, vp, ctypes.POINTER(ctypes.c_int)]),
         "msd_conv_relu_backward_k_noalloc": (i, [i, T, T, T, vp, i, i, vp]),
@@ -89,7 +90,7 @@ EXPORTED = [
     "msd_slab_layer_forward", "msd_slab_layer_backward",
     "msd_final_forward", "msd_final_backward", "msd_final_workspace_bytes",
     "msd_tuning_num_variants", "msd_tuning_set", "msd_tuning_get",
-    "msd_launch_count", "msd_fast_launch_count", "msd_split_launch_count", "msd_reset_launch_count", "msd_device_status",
+    "msd_launch_count", "msd_fast_launch_count", "msd_split_launch_count", "msd_mma_launch_count", "msd_reset_launch_count", "msd_device_status",
     "msd_conv_relu_backward_k_noalloc", "msd_noalloc_scratch_bytes", "msd_selftest_wait_timeout",
 ]
 

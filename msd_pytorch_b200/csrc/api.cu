@@ -17,12 +17,13 @@ void set_error(const char *fmt, ...) {
     va_end(ap);
 }
 
-static std::atomic<int64_t> g_launches{0}, g_fast_launches{0}, g_split_launches{0};
+static std::atomic<int64_t> g_launches{0}, g_fast_launches{0}, g_split_launches{0}, g_mma_launches{0};
 void count_launch(bool fast) {
     g_launches.fetch_add(1, std::memory_order_relaxed);
     if (fast) g_fast_launches.fetch_add(1, std::memory_order_relaxed);
 }
 void count_split_launch() { g_split_launches.fetch_add(1, std::memory_order_relaxed); }
+void count_mma_launch() { g_mma_launches.fetch_add(1, std::memory_order_relaxed); }
 
 static bool same_geometry(const View &a, const View &b) { return a.n == b.n && a.z == b.z && a.y == b.y && a.x == b.x; }
 
@@ -444,10 +445,12 @@ int msd_tuning_get(int family, int dilation) { return fast::tuning_get(family, d
 int64_t msd_launch_count(void) { return g_launches.load(); }
 int64_t msd_fast_launch_count(void) { return g_fast_launches.load(); }
 int64_t msd_split_launch_count(void) { return g_split_launches.load(); }
+int64_t msd_mma_launch_count(void) { return g_mma_launches.load(); }
 void msd_reset_launch_count(void) {
     g_launches.store(0);
     g_fast_launches.store(0);
     g_split_launches.store(0);
+    g_mma_launches.store(0);
 }
 
 }  // extern "C"

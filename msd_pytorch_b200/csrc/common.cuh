@@ -46,7 +46,8 @@ struct DeviceGuard {
 };
 
 void count_launch(bool fast);
-void count_split_launch();  // launches of the role-split 3D backward kernel (a subset of the tuned launches)
+void count_split_launch();
+void count_mma_launch();    // launches of the tensor-core 3D backward kernel (likewise)  // launches of the role-split 3D backward kernel (a subset of the tuned launches)
 
 // ---- kernel-side tensor view: N, C, then up to three spatial axes (Z, Y, X) ----
 // 2D tensors are stored with a unit Z axis so that one set of kernels serves both.

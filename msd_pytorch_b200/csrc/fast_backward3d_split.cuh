@@ -67,16 +67,17 @@ __device__ __forceinline__ void split_wait(uint64_t *bar, uint32_t parity, volat
 // floats) into the rows of m, in place: ReLU gate, plus the mirrored y / z sources next to
 // the volume's borders.  Cooperative over the kSplitBuilders builder threads (index btid); the
 // caller synchronises them afterwards.
+template <int NTHREADS = kSplitBuilders, int TR = kSplitRows>
 __device__ __forceinline__ void split_fill_rows(const BwdParams &p, float *rows, const float *orows, int HSLOT, int TXP, bool gate, int btid, int n,
                                                 int z, int y0, int x0) {
-    constexpr int RT = 9, TR = kSplitRows;
+    constexpr int RT = 9;
     const bool fold_rows = (y0 < p.d) || (y0 + TR + p.d > p.Y) || (z < p.d || z + p.d >= p.Z);
     if (!gate && !fold_rows) return;
     const float *go_n = p.gout + n * p.go_sn;
     const float *out_n = gate ? p.out + n * p.out_sn : nullptr;
     const int quads = TXP / 4;
 #pragma unroll 1
-    for (int item = btid; item < RT * TR * quads; item += kSplitBuilders) {
+    for (int item = btid; item < RT * TR * quads; item += NTHREADS) {
         const int rowid = item / quads, q4 = item - rowid * quads;
         const int rt = rowid / TR, rr = rowid - rt * TR;
         const int soff = rt * HSLOT + rr * TXP + 4 * q4;

@@ -1,5 +1,5 @@
 // 3D instantiations of the fused backward kernel (see fast_backward.cuh).
-#include "fast_backward3d_split.cuh"
+#include "fast_backward3d_mma.cuh"
 
 namespace msd {
 namespace fast {
@@ -25,6 +25,16 @@ static int launch3d_split(const CUtensorMap *m, const BwdParams &p, int grid, si
     return MSD_OK;
 }
 BwdLaunchFn bwd3d_split_launcher = launch3d_split;
+
+// tensor-core variant: maps[0] = activations (swizzled, channel as second dimension), maps[2] = gradient halo rows
+static int launch3d_mma(const CUtensorMap *m, const BwdParams &p, int grid, size_t smem, cudaStream_t s) {
+    auto kern = fused_backward3d_mma_kernel;
+    MSD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    MSD_CUDA_TRY(tma::launch_pdl(kern, dim3(grid), dim3(kMmaThreads), smem, s, m[0], m[2], p));
+    return MSD_OK;
+}
+BwdLaunchFn bwd3d_mma_launcher = launch3d_mma;
+size_t bwd3d_mma_smem(int C, int Dp, int stages) { return mma_layout(C, Dp, stages).total; }
 
 }  // namespace fast
 }  // namespace msd

@@ -8,7 +8,10 @@ int reduce_partials_f32(const float *partial, int nparts, int64_t pitch, int64_t
 }
 namespace fast {
 
-int get_tensor_map(int device, const void *ptr, int rank, const int64_t *dims, const int64_t *strides, const int *box, CUtensorMap *out);
+int get_tensor_map(int device, const void *ptr, int rank, const int64_t *dims, const int64_t *strides, const int *box, CUtensorMap *out,
+                   bool swizzle128 = false);
+extern BwdLaunchFn bwd3d_mma_launcher;
+size_t bwd3d_mma_smem(int C, int Dp, int stages);
 extern BwdLaunchFn bwd2d_launchers[2][2][3];
 extern BwdLaunchFn bwd3d_launchers[2][3];
 extern BwdLaunchFn bwd3d_split_launcher;
@@ -41,6 +44,7 @@ struct BwdPlan {
     int txq16, j, stages, blocks_per_sm;
     size_t smem;
     bool split;  // 3D kernel with X warps and K warps (fast_backward3d_split.cuh)
+    bool mma;    // 3D kernel on the tensor cores (fast_backward3d_mma.cuh)
 };
 
 // geometry of the role-split 3D kernel (the constants of the same names there)
@@ -48,6 +52,8 @@ static const int kSplitRows = 4, kSplitKWarps = 8, kSplitCB = 4, kSplitMaxDilati
 // below this many input channels the per-tile set-up of the split kernel outweighs its faster
 // channel loop (large dilations have more border tiles, whose set-up reads global memory)
 static int split_min_channels(int d) { return d <= 5 ? 8 : 12; }
+// tensor-core kernel (fast_backward3d_mma.cuh): rows per tile, most ring stages, fewest channels
+static const int kMmaRowsHost = 2, kMmaMaxStagesHost = 6, kMmaMinChannels = 8;
 
 static bool plan(const BackwardArgs &a, BwdPlan *pl) {
     const View &g = *a.gout;
@@ -58,6 +64,18 @@ static bool plan(const BackwardArgs &a, BwdPlan *pl) {
     const int Dp = (a.d + 3) & ~3;
     pl->txq16 = g.x <= 64 ? 1 : 0;
     pl->split = false;
+    pl->mma = false;
+    if (nd == 3 && do_x && do_k && !a.out && (g.x % 128) == 0 && a.d <= kSplitMaxDilation && C >= kMmaMinChannels && C <= 128 &&
+        tuning_get(BWD3D, a.d) == 2) {
+        // tensor-core kernel: tiles of 2 rows x 128 columns, stages of 64 voxels x all channels
+        for (int s = kMmaMaxStagesHost; s >= 2; --s) {
+            const size_t need = bwd3d_mma_smem((int)C, Dp, s);
+            if (need <= (size_t)227 * 1024) {
+                pl->j = 1, pl->stages = s, pl->blocks_per_sm = 1, pl->smem = need, pl->mma = true;
+                return true;
+            }
+        }
+    }
     const int TX = pl->txq16 ? 64 : 128;
     if (nd == 3 && do_x && do_k && (g.x % 128) == 0 && a.d <= kSplitMaxDilation && C >= split_min_channels(a.d) && tuning_get(BWD3D, a.d) != 0) {
         // role-split kernel: 4 X warps + 8 K warps on tiles of 4 rows x 128 columns, kSplitCB
@@ -243,7 +261,7 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
     p.N = (int)g.n, p.C = (int)C, p.Z = (int)g.z, p.Y = (int)g.y, p.X = (int)g.x;
     p.d = a.d, p.Dp = (a.d + 3) & ~3;
     const int TX = pl.txq16 ? 64 : 128;
-    const int TR = pl.split ? kSplitRows : (bwd_consumer_warps(a.nd) * 32 / (TX / 4)) * pl.j;
+    const int TR = pl.mma ? kMmaRowsHost : pl.split ? kSplitRows : (bwd_consumer_warps(a.nd) * 32 / (TX / 4)) * pl.j;
     get_z_window((int)g.z, &p.z0, &p.ZW);
     p.tiles_x = (int)ceil_div(g.x, TX);
     p.tiles_y = (int)ceil_div(g.y, TR);
@@ -274,6 +292,19 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
         const View *views[4] = {do_k ? a.in : a.gin, do_x ? a.gin : a.in, a.gout, a.out ? a.out : a.gout};
         for (int which = 0; which < 4; ++which) {
             const View *v = views[which];
+            if (pl.mma && (which == 1 || which == 3)) {  // the tensor-core kernel streams gin itself and needs no gate halo
+                maps[which] = maps[0];
+                continue;
+            }
+            if (pl.mma && which == 0) {
+                // activations as the tensor cores read them: boxes of 32 voxels x C8 channels x one row,
+                // the CHANNEL as second dimension, 128-byte swizzle
+                const int64_t dims[5] = {v->x, v->c, v->y, v->z, v->n}, strides[5] = {1, v->sc, v->sy, v->sz, v->sn};
+                const int box[5] = {32, (int)((C + 7) & ~7), 1, 1, 1};
+                int rc2 = get_tensor_map(device, v->p, 5, dims, strides, box, &maps[0], true);
+                if (rc2) return rc2;
+                continue;
+            }
             int box[5] = {which < 2 ? TX : TX + 2 * p.Dp, TR, 1, (pl.split && which < 2) ? kSplitCB : 1, 1};
             int64_t dims[5], strides[5];
             if (a.nd == 3) {
@@ -288,11 +319,12 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
         }
     }
     const int mode = do_x && do_k ? 2 : (do_k ? 1 : 0);
-    BwdLaunchFn fn = a.nd == 3 ? (pl.split ? bwd3d_split_launcher : bwd3d_launchers[pl.txq16][mode]) : bwd2d_launchers[pl.txq16][pl.j - 1][mode];
+    BwdLaunchFn fn = a.nd == 3 ? (pl.mma ? bwd3d_mma_launcher : pl.split ? bwd3d_split_launcher : bwd3d_launchers[pl.txq16][mode]) : bwd2d_launchers[pl.txq16][pl.j - 1][mode];
     int rc = fn(maps, p, grid, pl.smem, s);
     if (rc) return rc;
     count_launch(true);
     if (pl.split) count_split_launch();
+    if (pl.mma) count_mma_launch();
     if (do_k || do_b) {
         ReduceList single;
         ReduceList *list = a.defer ? a.defer : &single;

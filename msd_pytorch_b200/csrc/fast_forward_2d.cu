@@ -51,10 +51,13 @@ static uint64_t hash_key(const MapKey &k) {
 
 // Tiled descriptor over a float32 tensor; dims/strides innermost first, strides in elements
 // (strides[0] must be 1).  Descriptors are cached by (device, pointer, geometry, box).
-int get_tensor_map(int device, const void *ptr, int rank, const int64_t *dims, const int64_t *strides, const int *box, CUtensorMap *out) {
+// `swizzle128`: the box's 128-byte rows land with their 16-byte chunks XOR-permuted by the row
+// index (the layout the tensor cores read); the innermost box extent must then be 32 floats.
+int get_tensor_map(int device, const void *ptr, int rank, const int64_t *dims, const int64_t *strides, const int *box, CUtensorMap *out,
+                   bool swizzle128) {
     MapKey key;
     memset(&key, 0, sizeof(key));
-    key.ptr = ptr, key.rank = rank, key.device = device;
+    key.ptr = ptr, key.rank = rank, key.device = device, key.pad = swizzle128 ? 1 : 0;
     for (int i = 0; i < rank; ++i) key.dims[i] = dims[i], key.strides[i] = strides[i], key.box[i] = box[i];
     const uint64_t h = hash_key(key);
     std::lock_guard<std::mutex> l(g_map_mu);
@@ -79,7 +82,7 @@ int get_tensor_map(int device, const void *ptr, int rank, const int64_t *dims, c
     }
     CUtensorMap m;
     CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void *>(ptr), gdim, gstr, bdim, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) MSD_FAIL(MSD_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
     if (g_map_count >= kMapSlots * 3 / 4) {
@@ -152,7 +155,7 @@ int num_variants(int family) {
         case FWD2D: return kNumFwd2dVariants;  // lattice rows x column segments x tile width
         case BWD2D: return 2;  // 4 / 8 voxels per thread
         case FWD3D: return kNumFwd3dVariants;  // 4 / 2 column segments per thread / more row stacks
-        case BWD3D: return 2;  // unsplit consumers / X warps + K warps
+        case BWD3D: return 3;  // unsplit consumers / X warps + K warps / tensor cores
         default: return 1;
     }
 }
@@ -206,12 +209,12 @@ int forward(bool relu, const View &in, const float *k, const float *bias, const 
         const int64_t dims[5] = {in.x, in.y, in.z, in.c, in.n};
         const int64_t strides[5] = {1, in.sy, in.sz, in.sc, in.sn};
         const int box[5] = {var->bw, var->bh, 1, 1, 1};
-        rc = get_tensor_map(device, in.p, 5, dims, strides, box, &map);
+        rc = get_tensor_map(device, in.p, 5, dims, strides, box, &map, false);
     } else {
         const int64_t dims[4] = {in.x, in.y, in.c, in.n};
         const int64_t strides[4] = {1, in.sy, in.sc, in.sn};
         const int box[4] = {var->bw, var->bh, 1, 1};
-        rc = get_tensor_map(device, in.p, 4, dims, strides, box, &map);
+        rc = get_tensor_map(device, in.p, 4, dims, strides, box, &map, false);
     }
     if (rc) return rc;
     Fwd2dParams p;

@@ -195,7 +195,7 @@ def test_backward3d_role_split_variant(cuda_device, sp, B, depth):
     from msd_pytorch_b200.msd_block import block_backward_, block_forward_
 
     dev = cuda_device
-    assert _lib.lib.msd_tuning_num_variants(_lib.FAMILY_BWD3D) == 2
+    assert _lib.lib.msd_tuning_num_variants(_lib.FAMILY_BWD3D) == 3
     torch.manual_seed(17)
     dil = [1 + (i % 10) for i in range(depth)]
     ws = [torch.randn(1, 1 + i, 3, 3, 3, device=dev) * (2.0 / (27 * (1 + i))) ** 0.5 for i in range(depth)]
@@ -303,3 +303,99 @@ def test_bounded_wait_runs_out_and_reports(cuda_device):
     cc.conv_relu_forward(x, torch.randn(1, 2, 3, 3, device=dev), torch.zeros(1, device=dev), y, 2)
     torch.cuda.synchronize()
     assert torch.isfinite(y).all() and _lib.device_status(dev) == 0
+
+
+def _force_bwd3d(L, lib, variant):
+    old = [L.msd_tuning_get(lib.FAMILY_BWD3D, d) for d in range(1, 13)]
+    for d in range(1, 13):
+        assert L.msd_tuning_set(lib.FAMILY_BWD3D, d, variant) == 0
+    return old
+
+
+def _restore_bwd3d(L, lib, old):
+    for d, v in zip(range(1, 13), old):
+        L.msd_tuning_set(lib.FAMILY_BWD3D, d, v)
+
+
+@pytest.mark.parametrize("C,d,sp", [(8, 1, (6, 8, 128)), (24, 3, (7, 10, 128)), (50, 2, (5, 9, 256)), (50, 10, (12, 11, 128)), (64, 4, (4, 6, 128)),
+                                    (80, 5, (6, 6, 128)), (104, 12, (13, 14, 128))],
+                         ids=["c8_d1", "c24_d3", "c50_d2_x256", "c50_d10", "c64_d4", "c80_d5", "c104_d12"])
+def test_backward3d_tensor_core_variant_single_layer(cuda_device, C, d, sp):
+    """One layer's fused backward on the tensor cores (3D backward variant 2: TF32 MMAs with
+    error-compensated operand splitting) against the float64 CPU oracle, gradient tolerances of
+    the parity gate; input gradient and weight gradient are reported separately."""
+    from oracle import msd_oracle as O
+    from msd_pytorch_b200 import _lib
+    from msd_pytorch_b200.msd_block import block_backward_
+
+    dev = cuda_device
+    L = _lib.lib
+    g = torch.Generator().manual_seed(1000 + C + d)
+    res = torch.randn(1, C + 1, *sp, generator=g)
+    res[:, C] = torch.relu(res[:, C])                      # the layer's output channel: about half the gates closed
+    grad = torch.randn(1, C + 1, *sp, generator=g)
+    w = torch.randn(1, C, 3, 3, 3, generator=g) * (2.0 / (27 * C)) ** 0.5
+    gx_o = grad[:, :C].double().clone()
+    gk_o = torch.zeros(1, C, 3, 3, 3, dtype=torch.float64)
+    gb_o = torch.zeros(1, dtype=torch.float64)
+    O.conv_relu_backward_x(res[:, C:].double(), grad[:, C:].double(), w.double(), gx_o, d)
+    O.conv_relu_backward_k(res[:, C:].double(), grad[:, C:].double(), res[:, :C].double(), gk_o, d)
+    O.conv_relu_backward_bias(res[:, C:].double(), grad[:, C:].double(), gb_o)
+    old = _force_bwd3d(L, _lib, 2)
+    try:
+        n0 = L.msd_mma_launch_count()
+        rd, gd, wd = res.to(dev), grad.to(dev), w.to(dev)
+        gw, gb = torch.zeros_like(wd), torch.zeros(1, device=dev)
+        block_backward_(rd, gd, C, [d], [wd], [gw], gb)
+        torch.cuda.synchronize()
+        assert _lib.device_status(dev) == 0
+        assert L.msd_mma_launch_count() - n0 == 1, "the tensor-core kernel did not run"
+    finally:
+        _restore_bwd3d(L, _lib, old)
+
+    def worst(a, e):
+        e = e.double()
+        return float(((a.double().cpu() - e).abs() / (e.abs() + e.pow(2).mean().sqrt())).max())
+
+    print("tensor-core backward C=%d d=%d: worst relative deviation gin %.3g, gk %.3g, gb %.3g"
+          % (C, d, worst(gd[:, :C], gx_o), worst(gw, gk_o), worst(gb, gb_o)))
+    assert_close(gd[:, :C], gx_o, 1e-3, "grad_input")
+    assert_close(gw, gk_o, 1e-3, "grad_kernel")
+    assert_close(gb, gb_o, 1e-3, "grad_bias")
+    assert worst(gd[:, :C], gx_o) < 2e-5 and worst(gw, gk_o) < 2e-5, "3xTF32 should be as accurate as float32"
+
+
+def test_backward3d_tensor_core_variant_in_a_block(cuda_device):
+    """A depth-22 block whose layers with 8 and more input channels run on the tensor cores,
+    against the float64 oracle (gated hand-over between the layers included)."""
+    from oracle import msd_oracle as O
+    from msd_pytorch_b200 import _lib
+    from msd_pytorch_b200.msd_block import msd_block
+
+    dev = cuda_device
+    L = _lib.lib
+    depth, sp = 22, (12, 22, 128)
+    dil = [1 + (i % 10) for i in range(depth)]
+    g = torch.Generator().manual_seed(77)
+    x = torch.randn(1, 1, *sp, generator=g)
+    ws = [torch.randn(1, 1 + i, 3, 3, 3, generator=g) * (2.0 / (27 * (1 + i))) ** 0.5 for i in range(depth)]
+    bias = 0.05 * torch.randn(depth, generator=g)
+    gout = torch.randn(1, 1 + depth, *sp, generator=g)
+    old = _force_bwd3d(L, _lib, 2)
+    try:
+        n0 = L.msd_mma_launch_count()
+        xd = x.to(dev).requires_grad_(True)
+        wd = [w.to(dev).requires_grad_(True) for w in ws]
+        bd = bias.to(dev).requires_grad_(True)
+        res = msd_block(xd, dil, bd, *wd)
+        res.backward(gout.to(dev))
+        torch.cuda.synchronize()
+        assert L.msd_mma_launch_count() - n0 == sum(1 for i in range(depth) if 1 + i >= 8)
+        assert _lib.device_status(dev) == 0
+    finally:
+        _restore_bwd3d(L, _lib, old)
+    gi_o, gb_o, gws_o = O.msd_block_backward(res.detach().double().cpu(), gout.double(), dil, bias.double(), [w.double() for w in ws])
+    assert_close(xd.grad, gi_o, 1e-3, "grad_input")
+    assert_close(bd.grad, gb_o, 1e-3, "grad_bias")
+    for i, (w, e) in enumerate(zip(wd, gws_o)):
+        assert_close(w.grad, e, 1e-3, "grad_weight%d" % i)
