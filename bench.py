@@ -693,6 +693,8 @@ def main():
     ap.add_argument("--no-autotune", action="store_true", help="use the library's default launch variants")
     ap.add_argument("--no-extra-configs", action="store_true", help="skip the c4 / c5_zslab records that follow the default config's line")
     ap.add_argument("--one-layer", default=None, metavar="CFG:CHANNELS:DILATION", help="time one layer's kernels (profiling target) and exit")
+    ap.add_argument("--force-variant", default=None, metavar="FAMILY=V[,FAMILY=V]",
+                    help="force a launch variant for all dilations (families: fwd2d, bwd2d, fwd3d, bwd3d); implies --no-autotune")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     cfg = CONFIGS[args.config]
@@ -711,6 +713,15 @@ def main():
     torch.cuda.set_device(device)
     torch.backends.cudnn.allow_tf32 = False
     torch.backends.cuda.matmul.allow_tf32 = False
+    if args.force_variant:
+        from msd_pytorch_b200 import _lib
+
+        args.no_autotune = True
+        fam = {"fwd2d": _lib.FAMILY_FWD2D, "bwd2d": _lib.FAMILY_BWD2D, "fwd3d": _lib.FAMILY_FWD3D, "bwd3d": _lib.FAMILY_BWD3D}
+        for item in args.force_variant.split(","):
+            name, v = item.split("=")
+            for d in range(0, 33):
+                _lib.check(_lib.lib.msd_tuning_set(fam[name], d, int(v)))
     if args.one_layer:
         run_one_layer(args.one_layer, device)
         return

@@ -24,7 +24,7 @@
 // Rows of In beyond the layer's channels (the MMA reads 64 or 128 rows) hold whatever follows
 // in shared memory; they only reach accumulator rows that are never read.
 //
-// Warps:  0-3 epilogue | 4 TMA producer of In | 5 MMA issuer | 6 TMA producer of the halo rows
+// Warps:  0-3 epilogue | 4 TMA producer of In and gin | 5 MMA issuer | 6 TMA producer of the halo rows
 //         7-8 splitters | 9-12 builders.  Every hand-over is an mbarrier with a bounded wait.
 //
 // Requirements (checked by the host): X a multiple of 128, dilation <= 12, both gradients
@@ -52,25 +52,28 @@ constexpr int kMmaTmemCols = 512;
 constexpr int kMmaD2Col = 0, kMmaD1Col = 64;  // D2: 64 columns; D1: two buffers of up to 128 columns
 
 struct MmaLayout {
-    int C8, C16, in_stage_bytes, w_bytes, hslot, halo_bytes;
+    int C8, C16, in_stage_bytes, gin_stage_bytes, w_bytes, hslot, halo_bytes;
     size_t total;
 };
-__host__ __device__ inline MmaLayout mma_layout(int C, int Dp, int stages) {
+__host__ __device__ inline MmaLayout mma_layout(int C, int Dp, int stages, int gin_stages) {
     MmaLayout L;
     L.C8 = (C + 7) & ~7;
     L.C16 = (C + 15) & ~15;
     L.in_stage_bytes = 2 * (kMmaSV / 32) * L.C8 * 128;  // hi chunks, then lo chunks
+    L.gin_stage_bytes = L.C8 * kMmaSV * 4;              // [channel][64 voxels], dense
     L.w_bytes = 2 * L.C16 * 128;                        // hi rows, then lo rows
     L.hslot = (kMmaRows * (kMmaTX + 2 * Dp) + 31) & ~31;
     L.halo_bytes = 9 * L.hslot * 4;
-    // header | In ring | tables (2 slots) | W | halo rows (2 buffers); 16 KB of slack after the In
-    // ring is provided by the tables themselves (the MMA may read 128 rows from a chunk's base)
-    L.total = (size_t)kMmaHeaderBytes + (size_t)stages * L.in_stage_bytes + 2 * kMmaTableBytes + ((L.w_bytes + 1023) & ~1023) + 2 * (size_t)L.halo_bytes;
+    // header | In ring | tables (2 slots) | W | halo rows (2 buffers) | gin ring; 16 KB of slack after
+    // the In ring is provided by the tables themselves (the MMA may read 128 rows from a chunk's base)
+    L.total = (size_t)kMmaHeaderBytes + (size_t)stages * L.in_stage_bytes + 2 * kMmaTableBytes + ((L.w_bytes + 1023) & ~1023) +
+              2 * (size_t)L.halo_bytes + (size_t)gin_stages * L.gin_stage_bytes;
     return L;
 }
 
 __global__ void __launch_bounds__(kMmaThreads, 1)
-fused_backward3d_mma_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_gout, const BwdParams p) {
+fused_backward3d_mma_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_gin,
+                            const __grid_constant__ CUtensorMap map_gout, const BwdParams p) {
     constexpr int RT = 9, TAPS = 27, TX = kMmaTX, TR = kMmaRows, SV = kMmaSV, SPT = kMmaStagesPerTile;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     uint64_t *full_in = reinterpret_cast<uint64_t *>(smem_raw);  // [kMmaMaxStages]
@@ -82,19 +85,22 @@ fused_backward3d_mma_kernel(const __grid_constant__ CUtensorMap map_in, const __
     uint64_t *table_empty = table_full + 2;          // [2]
     uint64_t *d1_full = table_empty + 2;             // [2]
     uint64_t *d1_empty = d1_full + 2;                // [2]
-    uint64_t *final_bar = d1_empty + 2;
+    uint64_t *gin_full = d1_empty + 2;               // [kMmaMaxStages]
+    uint64_t *gin_empty = gin_full + kMmaMaxStages;  // [kMmaMaxStages]
+    uint64_t *final_bar = gin_empty + kMmaMaxStages;
     volatile int *abort_flag = reinterpret_cast<volatile int *>(final_bar + 1);
     uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(const_cast<int *>(abort_flag) + 1);
     float *red = reinterpret_cast<float *>(smem_raw + 512);  // bias partials of the builder warps
 
-    const int S = p.stages;
-    const MmaLayout L = mma_layout(p.C, p.Dp, S);
+    const int S = p.stages, SG = p.stages2;
+    const MmaLayout L = mma_layout(p.C, p.Dp, S, SG);
     const int C = p.C, C8 = L.C8, C16 = L.C16;
     const int TXP = TX + 2 * p.Dp, HSLOT = L.hslot;
     unsigned char *in_ring = smem_raw + kMmaHeaderBytes;
     unsigned char *tables = in_ring + (size_t)S * L.in_stage_bytes;
     unsigned char *wbuf = tables + 2 * kMmaTableBytes;
     float *halo = reinterpret_cast<float *>(wbuf + ((L.w_bytes + 1023) & ~1023));
+    unsigned char *gin_ring = reinterpret_cast<unsigned char *>(halo) + 2 * (size_t)L.halo_bytes;
     const int chunk_bytes = C8 * 128;               // one 32-voxel chunk of In: C8 rows of 128 bytes
     const int in_half = (SV / 32) * chunk_bytes;    // hi part of a stage; the lo part follows
 
@@ -109,6 +115,10 @@ fused_backward3d_mma_kernel(const __grid_constant__ CUtensorMap map_in, const __
             tma::mbar_init(&full_in[s], 1);
             tma::mbar_init(&in_ready[s], 1);
             tma::mbar_init(&empty_in[s], 1);
+        }
+        for (int s = 0; s < SG; ++s) {
+            tma::mbar_init(&gin_full[s], 1);
+            tma::mbar_init(&gin_empty[s], kMmaEpilogueWarps);
         }
         for (int i = 0; i < 2; ++i) {
             tma::mbar_init(&halo_full[i], 1);
@@ -156,6 +166,7 @@ fused_backward3d_mma_kernel(const __grid_constant__ CUtensorMap map_in, const __
         // ------------------------- TMA producer of the activations -------------------------
         if (lane == 0) {
             tma::prefetch_tensormap(&map_in);
+            tma::prefetch_tensormap(&map_gin);
             uint32_t it = 0;
             for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
                 int n, z, y0, x0;
@@ -168,6 +179,11 @@ fused_backward3d_mma_kernel(const __grid_constant__ CUtensorMap map_in, const __
                     // coordinates (x, channel, y, z, n); channels past C are zero-filled
 #pragma unroll
                     for (int j = 0; j < SV / 32; ++j) tma::tensor_g2s_5d(dst + j * chunk_bytes, &map_in, x0 + SV * h + 32 * j, 0, y0 + r, z, n, &full_in[s]);
+                    // the same voxels of every channel of the gradients, for the epilogue
+                    const int sg = it % SG;
+                    if (it >= (uint32_t)SG) tma::wait_parity(&gin_empty[sg], ((it / SG) & 1u) ^ 1u, abort_flag, p.status, 22);
+                    tma::mbar_arrive_expect_tx(&gin_full[sg], (uint32_t)L.gin_stage_bytes);
+                    tma::tensor_g2s_5d(gin_ring + (size_t)sg * L.gin_stage_bytes, &map_gin, x0 + SV * h, y0 + r, z, 0, n, &gin_full[sg]);
                 }
             }
         }
@@ -330,30 +346,28 @@ fused_backward3d_mma_kernel(const __grid_constant__ CUtensorMap map_in, const __
                 const int64_t voff = (int64_t)(y0 + r) * p.gi_sy + x0 + SV * h + vox;
                 float *gp = p.gin + n * p.gi_sn + z * p.gi_sz + voff;
                 const float *ip = p.in + n * p.in_sn + z * p.in_sz + (int64_t)(y0 + r) * p.in_sy + x0 + SV * h + vox;
-                // the gradients this thread will update, requested before the product is awaited
-                float g[16], gn[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) g[i] = (valid && i < C) ? gp[(int64_t)i * p.gi_sc] : 0.f;
+                const int sg = it % SG;
+                const float *gs = reinterpret_cast<const float *>(gin_ring + (size_t)sg * L.gin_stage_bytes) + vox;  // gs[c * 64]
+                tma::wait_parity(&gin_full[sg], (it / SG) & 1u, abort_flag, p.status, 23);
                 tma::wait_parity(&d1_full[buf], (it >> 1) & 1u, abort_flag, p.status, 19);
                 umma::fence_after_sync();
                 const bool live = valid && !*abort_flag;
                 const uint32_t d1 = tmem + kMmaD1Col + buf * 128 + ((uint32_t)(32 * warp) << 16);
                 for (int c0 = 0; c0 < C16; c0 += 16) {
-                    if (c0 + 16 < C16) {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) gn[i] = (valid && c0 + 16 + i < C) ? gp[(int64_t)(c0 + 16 + i) * p.gi_sc] : 0.f;
-                    }
                     float acc[16];
                     umma::tmem_ld16(d1 + c0, acc);
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const int c = c0 + i;
-                        float v = g[i] + acc[i];
-                        if (c == p.mask_channel && live) v = ip[(int64_t)c * p.in_sc] > 0.f ? v : 0.f;  // hand the layer below a gated gradient
-                        if (live && c < C) gp[(int64_t)c * p.gi_sc] = v;
-                        g[i] = gn[i];
+                        if (c < C) {
+                            float v = gs[c * SV] + acc[i];
+                            if (c == p.mask_channel && live) v = ip[(int64_t)c * p.in_sc] > 0.f ? v : 0.f;  // hand the layer below a gated gradient
+                            if (live) gp[(int64_t)c * p.gi_sc] = v;
+                        }
                     }
                 }
+                __syncwarp();
+                if (lane == 0) tma::mbar_arrive(&gin_empty[sg]);
                 umma::fence_before_sync();
                 __syncwarp();
                 if (lane == 0) tma::mbar_arrive(&d1_empty[buf]);

@@ -26,15 +26,16 @@ static int launch3d_split(const CUtensorMap *m, const BwdParams &p, int grid, si
 }
 BwdLaunchFn bwd3d_split_launcher = launch3d_split;
 
-// tensor-core variant: maps[0] = activations (swizzled, channel as second dimension), maps[2] = gradient halo rows
+// tensor-core variant: maps[0] = activations (swizzled, channel as second dimension), maps[1] = gradient tiles of all
+// channels, maps[2] = halo rows of the gradient channel
 static int launch3d_mma(const CUtensorMap *m, const BwdParams &p, int grid, size_t smem, cudaStream_t s) {
     auto kern = fused_backward3d_mma_kernel;
     MSD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    MSD_CUDA_TRY(tma::launch_pdl(kern, dim3(grid), dim3(kMmaThreads), smem, s, m[0], m[2], p));
+    MSD_CUDA_TRY(tma::launch_pdl(kern, dim3(grid), dim3(kMmaThreads), smem, s, m[0], m[1], m[2], p));
     return MSD_OK;
 }
 BwdLaunchFn bwd3d_mma_launcher = launch3d_mma;
-size_t bwd3d_mma_smem(int C, int Dp, int stages) { return mma_layout(C, Dp, stages).total; }
+size_t bwd3d_mma_smem(int C, int Dp, int stages, int gin_stages) { return mma_layout(C, Dp, stages, gin_stages).total; }
 
 }  // namespace fast
 }  // namespace msd

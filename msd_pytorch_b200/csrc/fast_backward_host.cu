@@ -11,7 +11,7 @@ namespace fast {
 int get_tensor_map(int device, const void *ptr, int rank, const int64_t *dims, const int64_t *strides, const int *box, CUtensorMap *out,
                    bool swizzle128 = false);
 extern BwdLaunchFn bwd3d_mma_launcher;
-size_t bwd3d_mma_smem(int C, int Dp, int stages);
+size_t bwd3d_mma_smem(int C, int Dp, int stages, int gin_stages);
 extern BwdLaunchFn bwd2d_launchers[2][2][3];
 extern BwdLaunchFn bwd3d_launchers[2][3];
 extern BwdLaunchFn bwd3d_split_launcher;
@@ -41,7 +41,7 @@ static bool aligned_view(const View *v) {
 }
 
 struct BwdPlan {
-    int txq16, j, stages, blocks_per_sm;
+    int txq16, j, stages, stages2, blocks_per_sm;
     size_t smem;
     bool split;  // 3D kernel with X warps and K warps (fast_backward3d_split.cuh)
     bool mma;    // 3D kernel on the tensor cores (fast_backward3d_mma.cuh)
@@ -68,13 +68,16 @@ static bool plan(const BackwardArgs &a, BwdPlan *pl) {
     if (nd == 3 && do_x && do_k && !a.out && (g.x % 128) == 0 && a.d <= kSplitMaxDilation && C >= kMmaMinChannels && C <= 128 &&
         tuning_get(BWD3D, a.d) == 2) {
         // tensor-core kernel: tiles of 2 rows x 128 columns, stages of 64 voxels x all channels
-        for (int s = kMmaMaxStagesHost; s >= 2; --s) {
-            const size_t need = bwd3d_mma_smem((int)C, Dp, s);
-            if (need <= (size_t)227 * 1024) {
-                pl->j = 1, pl->stages = s, pl->blocks_per_sm = 1, pl->smem = need, pl->mma = true;
-                return true;
+        // ring depths: as many stages of activations (hi + lo, 4 x the bytes of a gradient stage) as fit
+        // beside at least two, at most four stages of gradients
+        for (int s = kMmaMaxStagesHost; s >= 2; --s)
+            for (int sg = 4; sg >= 2; --sg) {
+                const size_t need = bwd3d_mma_smem((int)C, Dp, s, sg);
+                if (need <= (size_t)227 * 1024) {
+                    pl->j = 1, pl->stages = s, pl->stages2 = sg, pl->blocks_per_sm = 1, pl->smem = need, pl->mma = true;
+                    return true;
+                }
             }
-        }
     }
     const int TX = pl->txq16 ? 64 : 128;
     if (nd == 3 && do_x && do_k && (g.x % 128) == 0 && a.d <= kSplitMaxDilation && C >= split_min_channels(a.d) && tuning_get(BWD3D, a.d) != 0) {
@@ -267,6 +270,7 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
     p.tiles_y = (int)ceil_div(g.y, TR);
     p.num_tiles = (long long)p.tiles_x * p.tiles_y * p.ZW * g.n;
     p.stages = pl.stages;
+    p.stages2 = pl.mma ? pl.stages2 : 0;
     p.mask_channel = (do_x && do_k) ? a.mask_channel : -1;
     p.status = tma::device_status_ptr(device);
     if (!p.status) MSD_FAIL(MSD_ERR_CUDA, "fused backward: cannot locate the device status word");
@@ -292,8 +296,15 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
         const View *views[4] = {do_k ? a.in : a.gin, do_x ? a.gin : a.in, a.gout, a.out ? a.out : a.gout};
         for (int which = 0; which < 4; ++which) {
             const View *v = views[which];
-            if (pl.mma && (which == 1 || which == 3)) {  // the tensor-core kernel streams gin itself and needs no gate halo
+            if (pl.mma && which == 3) {  // the tensor-core kernel needs no gate halo
                 maps[which] = maps[0];
+                continue;
+            }
+            if (pl.mma && which == 1) {  // gradient tiles: 64 voxels of one row, all channels
+                const int64_t dims[5] = {v->x, v->y, v->z, v->c, v->n}, strides[5] = {1, v->sy, v->sz, v->sc, v->sn};
+                const int box[5] = {64, 1, 1, (int)((C + 7) & ~7), 1};
+                int rc2 = get_tensor_map(device, v->p, 5, dims, strides, box, &maps[1]);
+                if (rc2) return rc2;
                 continue;
             }
             if (pl.mma && which == 0) {
