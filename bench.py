@@ -413,11 +413,17 @@ class SlabStep:
         self.bias = torch.zeros(self.depth, device=device)
         self.fw = (torch.randn(1, 1 + self.depth, generator=g) / (1 + self.depth) ** 0.5).to(device)
         self.fb = (0.1 * torch.randn(1, generator=g)).to(device)
-        # owned planes of input and target, U(0,1), seeded per rank
-        gd = torch.Generator(device=device).manual_seed(1000 + rank)
+        # owned planes of input and target, U(0,1), seeded per GLOBAL plane: the data (and so the
+        # loss) are the same however many ranks share the volume
         zo = loc["g1"] - loc["g0"]
-        self.x = torch.rand(1, zo, Y, X, device=device, generator=gd)
-        self.t = torch.rand(zo * Y * X, device=device, generator=gd)
+        self.x = torch.empty(1, zo, Y, X, device=device)
+        self.t = torch.empty(zo, Y, X, device=device)
+        gd = torch.Generator(device=device)
+        for k in range(zo):
+            gd.manual_seed(100000 + loc["g0"] + k)
+            self.x[0, k].copy_(torch.rand(Y, X, device=device, generator=gd))
+            self.t[k].copy_(torch.rand(Y, X, device=device, generator=gd))
+        self.t = self.t.view(-1)
         self.block.gradients = torch.empty_like(self.block.result)
         self.vox_rank = zo * Y * X
         self.vox_total = Z * Y * X
@@ -484,6 +490,7 @@ def run_slab(args, cfg, rank, world, device, steps, warmup, full=True):
     st = SlabStep(cfg, rank, world, device, size)
     timed = Timer(device, world)
     ms_step, launches, clocks = timed(st.step, steps, warmup, sample_clocks=True)
+    loss_value = float(st.step().item())
     ms_fwd, _, _ = timed(st.forward, max(1, steps // 2), 1)
     st.head()
     ms_bwd, _, _ = timed(st.backward, max(1, steps // 2), 1)
@@ -522,7 +529,7 @@ def run_slab(args, cfg, rank, world, device, steps, warmup, full=True):
     if not full:
         return {"workload": "c5: MSD 3D depth %d, one 1x%dx%dx%d volume, mse, fwd+bwd, z-slabs of %d planes per rank" % (depth, *zs, zs[0] // world),
                 "scaling": "strong", "n_gpus": world, "ms_per_step": round(ms_step, 3), "voxels_per_s": vox_total / (ms_step * 1e-3),
-                "steps": steps, "warmup": warmup, "fwd_ms": round(ms_fwd, 3), "bwd_ms": round(ms_bwd, 3), "exchange": exchange,
+                "steps": steps, "warmup": warmup, "fwd_ms": round(ms_fwd, 3), "bwd_ms": round(ms_bwd, 3), "exchange": exchange, "loss": loss_value,
                 "roofline_frac_fwd": round(gbs_fwd / peak, 4), "roofline_frac_bwd": round(gbs_bwd / peak, 4),
                 "roofline_frac_step": round((a_fwd + a_bwd) / (ms_step * 1e-3) / 1e9 / peak, 4),
                 "gpu_launches": launches[0], "device_status": status, "clocks": clocks}
@@ -542,7 +549,7 @@ def run_slab(args, cfg, rank, world, device, steps, warmup, full=True):
         "roofline_forward": {"kernel": "forward2d_kernel<NT=3> + zgather_kernel", "bound": "hbm", "achieved": gbs_fwd, "peak": peak,
                              "unit": "GB/s", "frac": gbs_fwd / peak},
         "block_only": {"fwd_ms": ms_fwd, "bwd_ms": ms_bwd},
-        "exchange": exchange,
+        "exchange": exchange, "loss": loss_value,
     }
 
 
