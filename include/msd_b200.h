@@ -223,9 +223,10 @@ MSD_API int msd_slab_layer_backward(const msd_tensor_t *result, const msd_tensor
  * 3D backward: variant 0 = one kind of consumer warp computes both gradients,
  * variant 1 (default) = warps split by role (input-gradient warps, weight-gradient
  * warps, table builders) for layers with 8 (dilation <= 5) or 12 and more input
- * channels whose x extent is a multiple of 128; variant 2 = both gradients as TF32
- * tensor-core contractions with error-compensated operand splitting (tcgen05; 8 to
- * 128 input channels, x extent a multiple of 128, already gated gradient). */
+ * channels whose x extent is a multiple of 128; variant 2 = the input gradient as a
+ * TF32 tensor-core contraction with error-compensated operand splitting (tcgen05,
+ * float32-level accuracy), the weight gradient on the CUDA cores (8 to ~88 input
+ * channels, x extent a multiple of 128, already gated gradient). */
 MSD_API int msd_tuning_num_variants(int family);
 
 /* Force variant `variant` (or -1 = library default) for (family, dilation).

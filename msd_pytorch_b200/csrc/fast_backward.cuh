@@ -66,7 +66,6 @@ struct BwdParams {
     int tiles_x, tiles_y;
     long long num_tiles;
     int stages;
-    int stages2;  // ring stages of the gradient tiles (tensor-core 3D kernel only)
     int mask_channel;  // input channel whose new gradient is stored already gated by in[c] > 0 (-1: none)
     int *status;
 };

@@ -1,5 +1,5 @@
 // 3D instantiations of the fused backward kernel (see fast_backward.cuh).
-#include "fast_backward3d_mma.cuh"
+#include "fast_backward3d_hybrid.cuh"
 
 namespace msd {
 namespace fast {
@@ -26,16 +26,16 @@ static int launch3d_split(const CUtensorMap *m, const BwdParams &p, int grid, si
 }
 BwdLaunchFn bwd3d_split_launcher = launch3d_split;
 
-// tensor-core variant: maps[0] = activations (swizzled, channel as second dimension), maps[1] = gradient tiles of all
-// channels, maps[2] = halo rows of the gradient channel
-static int launch3d_mma(const CUtensorMap *m, const BwdParams &p, int grid, size_t smem, cudaStream_t s) {
-    auto kern = fused_backward3d_mma_kernel;
+// tensor-core variant: maps[0] = activation stages (4 channels x 2 rows x 128), maps[1] = L2 prefetch box of the
+// gradient tiles, maps[2] = halo rows of the gradient channel
+static int launch3d_hybrid(const CUtensorMap *m, const BwdParams &p, int grid, size_t smem, cudaStream_t s) {
+    auto kern = fused_backward3d_hybrid_kernel;
     MSD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    MSD_CUDA_TRY(tma::launch_pdl(kern, dim3(grid), dim3(kMmaThreads), smem, s, m[0], m[1], m[2], p));
+    MSD_CUDA_TRY(tma::launch_pdl(kern, dim3(grid), dim3(kHybThreads), smem, s, m[0], m[1], m[2], p));
     return MSD_OK;
 }
-BwdLaunchFn bwd3d_mma_launcher = launch3d_mma;
-size_t bwd3d_mma_smem(int C, int Dp, int stages, int gin_stages) { return mma_layout(C, Dp, stages, gin_stages).total; }
+BwdLaunchFn bwd3d_hybrid_launcher = launch3d_hybrid;
+size_t bwd3d_hybrid_smem(int C, int Dp, int stages) { return hyb_layout(C, Dp, stages).total; }
 
 }  // namespace fast
 }  // namespace msd

@@ -10,8 +10,8 @@ namespace fast {
 
 int get_tensor_map(int device, const void *ptr, int rank, const int64_t *dims, const int64_t *strides, const int *box, CUtensorMap *out,
                    bool swizzle128 = false);
-extern BwdLaunchFn bwd3d_mma_launcher;
-size_t bwd3d_mma_smem(int C, int Dp, int stages, int gin_stages);
+extern BwdLaunchFn bwd3d_hybrid_launcher;
+size_t bwd3d_hybrid_smem(int C, int Dp, int stages);
 extern BwdLaunchFn bwd2d_launchers[2][2][3];
 extern BwdLaunchFn bwd3d_launchers[2][3];
 extern BwdLaunchFn bwd3d_split_launcher;
@@ -41,10 +41,10 @@ static bool aligned_view(const View *v) {
 }
 
 struct BwdPlan {
-    int txq16, j, stages, stages2, blocks_per_sm;
+    int txq16, j, stages, blocks_per_sm;
     size_t smem;
     bool split;  // 3D kernel with X warps and K warps (fast_backward3d_split.cuh)
-    bool mma;    // 3D kernel on the tensor cores (fast_backward3d_mma.cuh)
+    bool mma;    // 3D kernel with the input gradient on the tensor cores (fast_backward3d_hybrid.cuh)
 };
 
 // geometry of the role-split 3D kernel (the constants of the same names there)
@@ -52,8 +52,8 @@ static const int kSplitRows = 4, kSplitKWarps = 8, kSplitCB = 4, kSplitMaxDilati
 // below this many input channels the per-tile set-up of the split kernel outweighs its faster
 // channel loop (large dilations have more border tiles, whose set-up reads global memory)
 static int split_min_channels(int d) { return d <= 5 ? 8 : 12; }
-// tensor-core kernel (fast_backward3d_mma.cuh): rows per tile, most ring stages, fewest channels
-static const int kMmaRowsHost = 2, kMmaMaxStagesHost = 6, kMmaMinChannels = 8;
+// tensor-core kernel (fast_backward3d_hybrid.cuh): rows per tile, channels per ring stage, most ring stages, fewest channels
+static const int kMmaRowsHost = 2, kMmaCBHost = 4, kMmaMaxStagesHost = 12, kMmaMinChannels = 8;
 
 static bool plan(const BackwardArgs &a, BwdPlan *pl) {
     const View &g = *a.gout;
@@ -67,17 +67,14 @@ static bool plan(const BackwardArgs &a, BwdPlan *pl) {
     pl->mma = false;
     if (nd == 3 && do_x && do_k && !a.out && (g.x % 128) == 0 && a.d <= kSplitMaxDilation && C >= kMmaMinChannels && C <= 128 &&
         tuning_get(BWD3D, a.d) == 2) {
-        // tensor-core kernel: tiles of 2 rows x 128 columns, stages of 64 voxels x all channels
-        // ring depths: as many stages of activations (hi + lo, 4 x the bytes of a gradient stage) as fit
-        // beside at least two, at most four stages of gradients
-        for (int s = kMmaMaxStagesHost; s >= 2; --s)
-            for (int sg = 4; sg >= 2; --sg) {
-                const size_t need = bwd3d_mma_smem((int)C, Dp, s, sg);
-                if (need <= (size_t)227 * 1024) {
-                    pl->j = 1, pl->stages = s, pl->stages2 = sg, pl->blocks_per_sm = 1, pl->smem = need, pl->mma = true;
-                    return true;
-                }
+        // tensor-core kernel: tiles of 2 rows x 128 columns, ring stages of 4 channels
+        for (int s = kMmaMaxStagesHost; s >= 4; --s) {
+            const size_t need = bwd3d_hybrid_smem((int)C, Dp, s);
+            if (need <= (size_t)227 * 1024) {
+                pl->j = 1, pl->stages = s, pl->blocks_per_sm = 1, pl->smem = need, pl->mma = true;
+                return true;
             }
+        }
     }
     const int TX = pl->txq16 ? 64 : 128;
     if (nd == 3 && do_x && do_k && (g.x % 128) == 0 && a.d <= kSplitMaxDilation && C >= split_min_channels(a.d) && tuning_get(BWD3D, a.d) != 0) {
@@ -270,7 +267,6 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
     p.tiles_y = (int)ceil_div(g.y, TR);
     p.num_tiles = (long long)p.tiles_x * p.tiles_y * p.ZW * g.n;
     p.stages = pl.stages;
-    p.stages2 = pl.mma ? pl.stages2 : 0;
     p.mask_channel = (do_x && do_k) ? a.mask_channel : -1;
     p.status = tma::device_status_ptr(device);
     if (!p.status) MSD_FAIL(MSD_ERR_CUDA, "fused backward: cannot locate the device status word");
@@ -300,23 +296,14 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
                 maps[which] = maps[0];
                 continue;
             }
-            if (pl.mma && which == 1) {  // gradient tiles: 64 voxels of one row, all channels
+            if (pl.mma && which == 1) {  // L2 prefetch box of the gradients: a whole tile of 64 channels
                 const int64_t dims[5] = {v->x, v->y, v->z, v->c, v->n}, strides[5] = {1, v->sy, v->sz, v->sc, v->sn};
-                const int box[5] = {64, 1, 1, (int)((C + 7) & ~7), 1};
+                const int box[5] = {TX, TR, 1, 64, 1};
                 int rc2 = get_tensor_map(device, v->p, 5, dims, strides, box, &maps[1]);
                 if (rc2) return rc2;
                 continue;
             }
-            if (pl.mma && which == 0) {
-                // activations as the tensor cores read them: boxes of 32 voxels x C8 channels x one row,
-                // the CHANNEL as second dimension, 128-byte swizzle
-                const int64_t dims[5] = {v->x, v->c, v->y, v->z, v->n}, strides[5] = {1, v->sc, v->sy, v->sz, v->sn};
-                const int box[5] = {32, (int)((C + 7) & ~7), 1, 1, 1};
-                int rc2 = get_tensor_map(device, v->p, 5, dims, strides, box, &maps[0], true);
-                if (rc2) return rc2;
-                continue;
-            }
-            int box[5] = {which < 2 ? TX : TX + 2 * p.Dp, TR, 1, (pl.split && which < 2) ? kSplitCB : 1, 1};
+            int box[5] = {which < 2 ? TX : TX + 2 * p.Dp, TR, 1, (which < 2) ? (pl.split ? kSplitCB : pl.mma ? kMmaCBHost : 1) : 1, 1};
             int64_t dims[5], strides[5];
             if (a.nd == 3) {
                 dims[0] = v->x, dims[1] = v->y, dims[2] = v->z, dims[3] = v->c, dims[4] = v->n;
@@ -330,7 +317,7 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
         }
     }
     const int mode = do_x && do_k ? 2 : (do_k ? 1 : 0);
-    BwdLaunchFn fn = a.nd == 3 ? (pl.mma ? bwd3d_mma_launcher : pl.split ? bwd3d_split_launcher : bwd3d_launchers[pl.txq16][mode]) : bwd2d_launchers[pl.txq16][pl.j - 1][mode];
+    BwdLaunchFn fn = a.nd == 3 ? (pl.mma ? bwd3d_hybrid_launcher : pl.split ? bwd3d_split_launcher : bwd3d_launchers[pl.txq16][mode]) : bwd2d_launchers[pl.txq16][pl.j - 1][mode];
     int rc = fn(maps, p, grid, pl.smem, s);
     if (rc) return rc;
     count_launch(true);
