@@ -21,7 +21,7 @@
 // accumulation ("3xTF32"): the result is as accurate as a float32 FMA chain.
 //
 // Per tile of 2 rows x 128 columns (256 voxels):
-//   builders (2 warps)  halo rows of the gated gradient channel (TMA) -> rows of m -> the table
+//   builders (4 warps)  halo rows of the gated gradient channel (TMA) -> rows of m -> the table
 //                       M_t(voxel) twice: plain float32 [tap][voxel] for the K warps, and
 //                       [voxel][tap] as hi / lo with the 128-byte swizzle (B operand of the MMA)
 //   MMA issuer          12 x tcgen05.mma (M = 64 or 128 channels, N = 256) -> D in tensor memory
@@ -29,8 +29,8 @@
 //                       from L2 (the producer prefetches the tile's gin with a bulk L2 prefetch)
 //   K warps (8)         as in the role-split kernel: lane = (quarter-warp, tap lane), 4 taps x 16
 //                       voxels of M in registers, activations streamed through a TMA ring of
-//                       4-channel stages; the two halves of the K warps take alternate stages
-//   producer            TMA: activations ring, halo rows of the next tile, L2 prefetch of gin
+//                       8-channel stages; the two halves of the K warps take alternate stages
+//   producers (2 warps) TMA: activations ring | halo rows of the next tile, L2 prefetch of gin
 // The accumulator is double-buffered (2 x 256 of the 512 columns), so the MMA of the next tile
 // overlaps this tile's epilogue.  Every hand-over is an mbarrier with a time-bounded wait.
 //
@@ -44,11 +44,13 @@ namespace msd {
 namespace fast {
 
 constexpr int kHybTX = 128, kHybRows = 2, kHybNV = kHybTX * kHybRows;  // tile: 256 voxels = N of the MMA
-constexpr int kHybCB = 4;                                              // channels per ring stage
-constexpr int kHybThreads = 512;
-constexpr int kHybEpilogueWarps = 4, kHybKWarp0 = 4, kHybKWarps = 8, kHybProducerWarp = 12, kHybIssuerWarp = 13, kHybBuilderWarp0 = 14;
-constexpr int kHybBuilders = 64;
-constexpr int kHybMaxStages = 12;
+constexpr int kHybCB = 8;                                              // channels per ring stage
+constexpr int kHybThreads = 640;                                       // five warpgroups
+constexpr int kHybEpilogueWarps = 4, kHybKWarp0 = 4, kHybKWarps = 8, kHybProducerWarp = 12, kHybIssuerWarp = 13, kHybHaloWarp = 14, kHybBuilderWarp0 = 16;
+constexpr int kHybBuilders = 128;
+constexpr int kHybMaxStages = 8;
+// registers per thread after setmaxnreg: epilogue and K warpgroups 128, producer group 56, builders 72 (65536 in all)
+constexpr int kHybRegsMain = 128, kHybRegsProducer = 56, kHybRegsBuilder = 72;
 constexpr int kHybHeaderBytes = 1024;
 constexpr int kHybT1Bytes = kHybNV * 128;       // one copy (hi or lo) of T1[voxel][32 taps]
 constexpr int kHybTS = kHybNV + 4;              // tap stride of the plain table (4 banks apart)
@@ -160,47 +162,46 @@ fused_backward3d_hybrid_kernel(const __grid_constant__ CUtensorMap map_in, const
         x0 = tx_i * TX, y0 = ty_i * TR;
     };
 
+    if (warp >= kHybProducerWarp && warp < kHybBuilderWarp0) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kHybRegsProducer));
     if (warp == kHybProducerWarp) {
-        // ------------------------------------ TMA producer ------------------------------------
+        // ------------------------- TMA producer of the activations -------------------------
         if (lane == 0) {
             tma::prefetch_tensormap(&map_in);
-            tma::prefetch_tensormap(&map_gout);
-            tma::prefetch_tensormap(&map_gin_prefetch);
-            const uint32_t halo_bytes = (uint32_t)(RT * TR * TXP * 4);
-            auto issue_halo = [&](long long tile) {
+            uint32_t it = 0, s = 0, ph = 0;
+            for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
                 int n, z, y0, x0;
                 tile_coords(tile, n, z, y0, x0);
-                tma::mbar_arrive_expect_tx(halo_full, halo_bytes);
-#pragma unroll 1
-                for (int rt = 0; rt < RT; ++rt)
-                    tma::tensor_g2s_5d(rows + rt * HSLOT, &map_gout, x0 - p.Dp, y0 + p.d * (1 - rt % 3), z + p.d * (1 - rt / 3), 0, n, halo_full);
-            };
-            auto prefetch_gin = [&](long long tile) {  // the whole tile of every channel, into L2, for the epilogue
-                int n, z, y0, x0;
-                tile_coords(tile, n, z, y0, x0);
-                for (int c0 = 0; c0 < C; c0 += 64) prefetch_l2_5d(&map_gin_prefetch, x0, y0, z, c0, n);
-            };
-            uint32_t it = 0, tcount = 0, s = 0, ph = 0;
-            if ((long long)blockIdx.x < p.num_tiles) {
-                issue_halo(blockIdx.x);
-                prefetch_gin(blockIdx.x);
-            }
-            const int halo_at = (ngroups < S ? ngroups : S) - 1;
-            for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++tcount) {
-                int n, z, y0, x0;
-                tile_coords(tile, n, z, y0, x0);
-                if (tile + gridDim.x < p.num_tiles) prefetch_gin(tile + gridDim.x);
                 for (int g = 0; g < ngroups; ++g, ++it) {
                     if (it >= (uint32_t)S) split_wait(&empty[s], ph ^ 1u, abort_flag, p.status, 1);
                     tma::mbar_arrive_expect_tx(&full[s], (uint32_t)(STAGE * 4));
                     // channels past C are outside the tensor map: zero-filled, no traffic
                     tma::tensor_g2s_5d(ring + (size_t)s * STAGE, &map_in, x0, y0, z, g * CB, n, &full[s]);
-                    if (g == halo_at && tile + gridDim.x < p.num_tiles) {
-                        split_wait(halo_empty, tcount & 1u, abort_flag, p.status, 5);
-                        issue_halo(tile + gridDim.x);
-                    }
                     if (++s == (uint32_t)S) s = 0, ph ^= 1u;
                 }
+            }
+        }
+    } else if (warp == kHybHaloWarp) {
+        // ------------- TMA producer of the halo rows; L2 prefetch of the gradients -------------
+        if (lane == 0) {
+            tma::prefetch_tensormap(&map_gout);
+            tma::prefetch_tensormap(&map_gin_prefetch);
+            const uint32_t halo_bytes = (uint32_t)(RT * TR * TXP * 4);
+            auto prefetch_gin = [&](long long tile) {  // the whole tile of every channel, into L2, for the epilogue
+                int n, z, y0, x0;
+                tile_coords(tile, n, z, y0, x0);
+                for (int c0 = 0; c0 < C; c0 += 64) prefetch_l2_5d(&map_gin_prefetch, x0, y0, z, c0, n);
+            };
+            if ((long long)blockIdx.x < p.num_tiles) prefetch_gin(blockIdx.x);
+            uint32_t tc = 0;
+            for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++tc) {
+                int n, z, y0, x0;
+                tile_coords(tile, n, z, y0, x0);
+                if (tc) split_wait(halo_empty, (tc - 1) & 1u, abort_flag, p.status, 5);  // the builders are done with the previous rows
+                tma::mbar_arrive_expect_tx(halo_full, halo_bytes);
+#pragma unroll 1
+                for (int rt = 0; rt < RT; ++rt)
+                    tma::tensor_g2s_5d(rows + rt * HSLOT, &map_gout, x0 - p.Dp, y0 + p.d * (1 - rt % 3), z + p.d * (1 - rt / 3), 0, n, halo_full);
+                if (tile + gridDim.x < p.num_tiles) prefetch_gin(tile + gridDim.x);
             }
         }
     } else if (warp == kHybIssuerWarp) {
@@ -230,6 +231,7 @@ fused_backward3d_hybrid_kernel(const __grid_constant__ CUtensorMap map_in, const
         }
     } else if (warp >= kHybBuilderWarp0) {
         // ---------------- builders: the tables of the NEXT tile while the K warps stream ----------------
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kHybRegsBuilder));
         const int btid = tid - kHybBuilderWarp0 * 32, bw = btid >> 5;
         uint32_t tc = 0;
         float bsum = 0.f;
@@ -244,23 +246,33 @@ fused_backward3d_hybrid_kernel(const __grid_constant__ CUtensorMap map_in, const
             }
             tma::named_barrier(3, kHybBuilders);
             const bool fold_l = x0 == 0, fold_r = x0 + TX == p.X;
-            // one tap per warp and step; lanes on consecutive voxels (eight runs of 32)
+            // thread = voxel (two per thread): its 27 values of M from the nine rows, then one row of
+            // T1 as 128-bit stores (hi and lo) and 27 plain stores for the K warps
 #pragma unroll 1
-            for (int t = bw; t < TAPS; t += kHybBuilders / 32) {
-                const int rt = t / 3, tx = t - 3 * rt;
+            for (int vv = 0; vv < NV / kHybBuilders; ++vv) {
+                const int vox = btid + kHybBuilders * vv, r = vox / TX, ci = vox % TX;
+                float m[28];
 #pragma unroll
-                for (int k = 0; k < NV / 32; ++k) {
-                    const int vox = 32 * k + lane, r = vox / TX, ci = vox % TX;  // voxel of the tile, its row and column
-                    const float *row = rows + rt * HSLOT + r * TXP + p.Dp;       // row[i] <-> image x = x0 + i
-                    float v = row[ci - p.d * (tx - 1)];
-                    if (tx == 0 && fold_l && ci < p.d) v += row[p.d - 1 - ci];
-                    if (tx == 2 && fold_r && ci >= TX - p.d) v += row[2 * TX - 1 - p.d - ci];
-                    if (t == 13) bsum += v;
-                    msm[t * TS + vox] = v;
-                    const float hi = umma::tf32_hi(v);
-                    const uint32_t o = umma::sw128_offset(vox, t);
-                    *reinterpret_cast<float *>(t1 + o) = hi;
-                    *reinterpret_cast<float *>(t1 + kHybT1Bytes + o) = v - hi;
+                for (int rt = 0; rt < RT; ++rt) {
+                    const float *row = rows + rt * HSLOT + r * TXP + p.Dp;  // row[i] <-> image x = x0 + i
+                    float v0 = row[ci + p.d], v1 = row[ci], v2 = row[ci - p.d];
+                    if (fold_l && ci < p.d) v0 += row[p.d - 1 - ci];
+                    if (fold_r && ci >= TX - p.d) v2 += row[2 * TX - 1 - p.d - ci];
+                    m[3 * rt] = v0, m[3 * rt + 1] = v1, m[3 * rt + 2] = v2;
+                }
+                m[27] = 0.f;
+                bsum += m[13];
+#pragma unroll
+                for (int t = 0; t < TAPS; ++t) msm[t * TS + vox] = m[t];
+                unsigned char *row1 = t1 + vox * 128;
+#pragma unroll
+                for (int q = 0; q < 7; ++q) {
+                    float4 h4, l4;
+                    h4.x = umma::tf32_hi(m[4 * q]), h4.y = umma::tf32_hi(m[4 * q + 1]), h4.z = umma::tf32_hi(m[4 * q + 2]), h4.w = umma::tf32_hi(m[4 * q + 3]);
+                    l4.x = m[4 * q] - h4.x, l4.y = m[4 * q + 1] - h4.y, l4.z = m[4 * q + 2] - h4.z, l4.w = m[4 * q + 3] - h4.w;
+                    const int off = (q ^ (vox & 7)) << 4;
+                    *reinterpret_cast<float4 *>(row1 + off) = h4;
+                    *reinterpret_cast<float4 *>(row1 + kHybT1Bytes + off) = l4;
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // T1 is read by the tensor cores, the rows are rewritten by TMA
@@ -275,10 +287,11 @@ fused_backward3d_hybrid_kernel(const __grid_constant__ CUtensorMap map_in, const
             for (int off = 16; off > 0; off >>= 1) bsum += __shfl_down_sync(0xffffffffu, bsum, off);
             if (lane == 0) red[bw] = bsum;
             tma::named_barrier(3, kHybBuilders);
-            if (btid == 0 && !*abort_flag) p.part_b[blockIdx.x] = red[0] + red[1];
+            if (btid == 0 && !*abort_flag) p.part_b[blockIdx.x] = (red[0] + red[1]) + (red[2] + red[3]);
         }
-    } else if (warp >= kHybKWarp0) {
+    } else if (warp >= kHybKWarp0 && warp < kHybKWarp0 + kHybKWarps) {
         // ===================================== K warps =====================================
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kHybRegsMain));
         // unit = (row, half) of the tile: 64 voxels; the warps of parity 0 / 1 take the even / odd ring
         // stages.  lane = (qw, tl): taps tl + 8 {0..3}; voxels 4 (4 j + qw) + {0..3}, j = 0..3, of the unit.
         const int kw = warp - kHybKWarp0, unit = kw & 3, parity = kw >> 2, r = unit >> 1, h = unit & 1;
@@ -352,8 +365,9 @@ fused_backward3d_hybrid_kernel(const __grid_constant__ CUtensorMap map_in, const
                 if (++s == (uint32_t)S) s = 0, ph ^= 1u;
             }
         }
-    } else {
+    } else if (warp < kHybEpilogueWarps) {
         // ------------------------------------ epilogue warps ------------------------------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kHybRegsMain));
         // thread = channel.  M = 64: channel c sits in lane 32 (c / 16) + (c % 16) of the accumulator
         // (the upper half of each warp's lanes holds nothing); M = 128: in lane c.
         const int ch = L.mrows == 64 ? ((lane < 16) ? 16 * warp + lane : -1) : 32 * warp + lane;
@@ -368,7 +382,7 @@ fused_backward3d_hybrid_kernel(const __grid_constant__ CUtensorMap map_in, const
             const float *ibase = p.in + n * p.in_sn + (int64_t)cc * p.in_sc + z * p.in_sz + (int64_t)y0 * p.in_sy + x0;
             const bool gate_here = has_channel && ch == p.mask_channel;
             // 16 steps of 16 voxels; the gradients of three steps are in flight ahead of the sums
-            constexpr int STEPS = NV / 16, AHEAD = 3;
+            constexpr int STEPS = NV / 16, AHEAD = 4;
             float4 g[AHEAD][4];
             auto row_ok = [&](int q) { return has_channel && (y0 + (q * 16) / TX) < p.Y; };
             auto goff = [&](int q) { return (int64_t)((q * 16) / TX) * p.gi_sy + (q * 16) % TX; };
@@ -388,23 +402,27 @@ fused_backward3d_hybrid_kernel(const __grid_constant__ CUtensorMap map_in, const
             umma::fence_after_sync();
             const bool live = !*abort_flag;
             const uint32_t d = tmem + buf * NV + ((uint32_t)(32 * warp) << 16);
+            uint32_t acc[2][16];  // the sums of a step arrive while the previous step is added and stored
+            umma::tmem_ld16_issue(d, acc[0]);
 #pragma unroll
             for (int q = 0; q < STEPS; ++q) {
-                float acc[16];
-                umma::tmem_ld16(d + 16 * q, acc);
+                umma::tmem_ld_wait();
+                if (q + 1 < STEPS) umma::tmem_ld16_issue(d + 16 * (q + 1), acc[(q + 1) & 1]);
+                const uint32_t(&a)[16] = acc[q & 1];
                 float4(&cur)[4] = g[q % AHEAD];
                 float4 out[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
-                    out[i] = make_float4(cur[i].x + acc[4 * i], cur[i].y + acc[4 * i + 1], cur[i].z + acc[4 * i + 2], cur[i].w + acc[4 * i + 3]);
+                    out[i] = make_float4(cur[i].x + __uint_as_float(a[4 * i]), cur[i].y + __uint_as_float(a[4 * i + 1]),
+                                         cur[i].z + __uint_as_float(a[4 * i + 2]), cur[i].w + __uint_as_float(a[4 * i + 3]));
                 if (gate_here && row_ok(q)) {
                     // this channel is the output of the layer below: hand its gradient over gated
                     const float4 *a4 = reinterpret_cast<const float4 *>(ibase + (int64_t)((q * 16) / TX) * p.in_sy + (q * 16) % TX);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        const float4 a = a4[i];
-                        out[i].x = a.x > 0.f ? out[i].x : 0.f, out[i].y = a.y > 0.f ? out[i].y : 0.f;
-                        out[i].z = a.z > 0.f ? out[i].z : 0.f, out[i].w = a.w > 0.f ? out[i].w : 0.f;
+                        const float4 av = a4[i];
+                        out[i].x = av.x > 0.f ? out[i].x : 0.f, out[i].y = av.y > 0.f ? out[i].y : 0.f;
+                        out[i].z = av.z > 0.f ? out[i].z : 0.f, out[i].w = av.w > 0.f ? out[i].w : 0.f;
                     }
                 }
                 if (live && row_ok(q)) {

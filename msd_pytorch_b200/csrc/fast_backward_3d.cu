@@ -26,7 +26,7 @@ static int launch3d_split(const CUtensorMap *m, const BwdParams &p, int grid, si
 }
 BwdLaunchFn bwd3d_split_launcher = launch3d_split;
 
-// tensor-core variant: maps[0] = activation stages (4 channels x 2 rows x 128), maps[1] = L2 prefetch box of the
+// tensor-core variant: maps[0] = activation stages (8 channels x 2 rows x 128), maps[1] = L2 prefetch box of the
 // gradient tiles, maps[2] = halo rows of the gradient channel
 static int launch3d_hybrid(const CUtensorMap *m, const BwdParams &p, int grid, size_t smem, cudaStream_t s) {
     auto kern = fused_backward3d_hybrid_kernel;

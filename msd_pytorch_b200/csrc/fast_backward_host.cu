@@ -53,7 +53,7 @@ static const int kSplitRows = 4, kSplitKWarps = 8, kSplitCB = 4, kSplitMaxDilati
 // channel loop (large dilations have more border tiles, whose set-up reads global memory)
 static int split_min_channels(int d) { return d <= 5 ? 8 : 12; }
 // tensor-core kernel (fast_backward3d_hybrid.cuh): rows per tile, channels per ring stage, most ring stages, fewest channels
-static const int kMmaRowsHost = 2, kMmaCBHost = 4, kMmaMaxStagesHost = 12, kMmaMinChannels = 8;
+static const int kMmaRowsHost = 2, kMmaCBHost = 8, kMmaMaxStagesHost = 8, kMmaMinChannels = 8;
 
 static bool plan(const BackwardArgs &a, BwdPlan *pl) {
     const View &g = *a.gout;
@@ -67,8 +67,8 @@ static bool plan(const BackwardArgs &a, BwdPlan *pl) {
     pl->mma = false;
     if (nd == 3 && do_x && do_k && !a.out && (g.x % 128) == 0 && a.d <= kSplitMaxDilation && C >= kMmaMinChannels && C <= 128 &&
         tuning_get(BWD3D, a.d) == 2) {
-        // tensor-core kernel: tiles of 2 rows x 128 columns, ring stages of 4 channels
-        for (int s = kMmaMaxStagesHost; s >= 4; --s) {
+        // tensor-core kernel: tiles of 2 rows x 128 columns, ring stages of 8 channels
+        for (int s = kMmaMaxStagesHost; s >= 3; --s) {
             const size_t need = bwd3d_hybrid_smem((int)C, Dp, s);
             if (need <= (size_t)227 * 1024) {
                 pl->j = 1, pl->stages = s, pl->blocks_per_sm = 1, pl->smem = need, pl->mma = true;
