@@ -49,8 +49,12 @@ constexpr int kHybThreads = 640;                                       // five w
 constexpr int kHybEpilogueWarps = 4, kHybKWarp0 = 4, kHybKWarps = 8, kHybProducerWarp = 12, kHybIssuerWarp = 13, kHybHaloWarp = 14, kHybBuilderWarp0 = 16;
 constexpr int kHybBuilders = 128;
 constexpr int kHybMaxStages = 8;
-// registers per thread after setmaxnreg: epilogue and K warpgroups 128, producer group 56, builders 72 (65536 in all)
-constexpr int kHybRegsMain = 128, kHybRegsProducer = 56, kHybRegsBuilder = 72;
+// Registers per thread after setmaxnreg.  The pool that setmaxnreg re-divides is what the block got
+// at launch: 640 threads x 96 registers (the launch bound's 102, rounded down to a multiple of 8) =
+// 61440.  3 warpgroups x 128 threads x 120 + 128 x 40 + 128 x 72 = 60416 fits; a sum above the pool
+// would make setmaxnreg.inc wait forever.
+constexpr int kHybRegsMain = 120, kHybRegsProducer = 40, kHybRegsBuilder = 72;
+static_assert(3 * 128 * kHybRegsMain + 128 * kHybRegsProducer + 128 * kHybRegsBuilder <= kHybThreads * 96, "setmaxnreg budget exceeds the register pool");
 constexpr int kHybHeaderBytes = 1024;
 constexpr int kHybT1Bytes = kHybNV * 128;       // one copy (hi or lo) of T1[voxel][32 taps]
 constexpr int kHybTS = kHybNV + 4;              // tap stride of the plain table (4 banks apart)

@@ -30,6 +30,15 @@ BwdLaunchFn bwd3d_split_launcher = launch3d_split;
 // gradient tiles, maps[2] = halo rows of the gradient channel
 static int launch3d_hybrid(const CUtensorMap *m, const BwdParams &p, int grid, size_t smem, cudaStream_t s) {
     auto kern = fused_backward3d_hybrid_kernel;
+    // the kernel re-divides its registers between its warpgroups; refuse to launch a build whose
+    // register pool is smaller than what it will ask for (setmaxnreg.inc would wait forever)
+    static int pool_ok = -1;
+    if (pool_ok < 0) {
+        cudaFuncAttributes fa;
+        MSD_CUDA_TRY(cudaFuncGetAttributes(&fa, kern));
+        pool_ok = (fa.numRegs * kHybThreads >= 3 * 128 * kHybRegsMain + 128 * kHybRegsProducer + 128 * kHybRegsBuilder) ? 1 : 0;
+    }
+    if (!pool_ok) MSD_FAIL(MSD_ERR_UNSUPPORTED, "tensor-core 3D backward: this build's register allocation does not fit its warpgroup budgets");
     MSD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     MSD_CUDA_TRY(tma::launch_pdl(kern, dim3(grid), dim3(kHybThreads), smem, s, m[0], m[1], m[2], p));
     return MSD_OK;
