@@ -27,9 +27,10 @@
 //   MMA issuer          12 x tcgen05.mma (M = 64 or 128 channels, N = 256) -> D in tensor memory
 //   epilogue (4 warps)  thread = channel: D + gin -> gin, 64 bytes per thread and step, gin read
 //                       from L2 (the producer prefetches the tile's gin with a bulk L2 prefetch)
-//   K warps (8)         as in the role-split kernel: lane = (quarter-warp, tap lane), 4 taps x 16
-//                       voxels of M in registers, activations streamed through a TMA ring of
-//                       8-channel stages; the two halves of the K warps take alternate stages
+//   K warps (16)        like those of the role-split kernel, but with half the voxels each so that
+//                       twice as many fit: lane = (quarter-warp, tap lane), 4 taps x 8 voxels of M in
+//                       registers (32 of its 80), activations streamed through a TMA ring of 8-channel
+//                       stages; the two K warps of a 32-voxel unit take alternate stages
 //   producers (2 warps) TMA: activations ring | halo rows of the next tile, L2 prefetch of gin
 // The accumulator is double-buffered (2 x 256 of the 512 columns), so the MMA of the next tile
 // overlaps this tile's epilogue.  Every hand-over is an mbarrier with a time-bounded wait.
@@ -45,16 +46,19 @@ namespace fast {
 
 constexpr int kHybTX = 128, kHybRows = 2, kHybNV = kHybTX * kHybRows;  // tile: 256 voxels = N of the MMA
 constexpr int kHybCB = 8;                                              // channels per ring stage
-constexpr int kHybThreads = 640;                                       // five warpgroups
-constexpr int kHybEpilogueWarps = 4, kHybKWarp0 = 4, kHybKWarps = 8, kHybProducerWarp = 12, kHybIssuerWarp = 13, kHybHaloWarp = 14, kHybBuilderWarp0 = 16;
+constexpr int kHybThreads = 896;                                       // seven warpgroups
+constexpr int kHybKUnits = 8;                                          // units of 32 voxels per tile; two K warps (alternate stages) each
+constexpr int kHybEpilogueWarps = 4, kHybKWarp0 = 4, kHybKWarps = 2 * kHybKUnits, kHybProducerWarp = 20, kHybIssuerWarp = 21, kHybHaloWarp = 22,
+              kHybBuilderWarp0 = 24;
 constexpr int kHybBuilders = 128;
 constexpr int kHybMaxStages = 8;
 // Registers per thread after setmaxnreg.  The pool that setmaxnreg re-divides is what the block got
-// at launch: 640 threads x 96 registers (the launch bound's 102, rounded down to a multiple of 8) =
-// 61440.  3 warpgroups x 128 threads x 120 + 128 x 40 + 128 x 72 = 60416 fits; a sum above the pool
-// would make setmaxnreg.inc wait forever.
-constexpr int kHybRegsMain = 120, kHybRegsProducer = 40, kHybRegsBuilder = 72;
-static_assert(3 * 128 * kHybRegsMain + 128 * kHybRegsProducer + 128 * kHybRegsBuilder <= kHybThreads * 96, "setmaxnreg budget exceeds the register pool");
+// at launch: 896 threads x 72 registers (the launch bound's 73, rounded down to a multiple of 8) =
+// 64512 = 128 x (96 epilogue + 4 x 80 K warpgroups + 24 producers + 64 builders).  A sum above the
+// pool would make setmaxnreg.inc wait forever; the launcher checks the compiled kernel against it.
+constexpr int kHybRegsEpilogue = 96, kHybRegsK = 80, kHybRegsProducer = 24, kHybRegsBuilder = 64;
+constexpr int kHybRegBudget = 128 * (kHybRegsEpilogue + (kHybKWarps / 4) * kHybRegsK + kHybRegsProducer + kHybRegsBuilder);
+static_assert(kHybRegBudget <= kHybThreads * 72, "setmaxnreg budget exceeds the register pool");
 constexpr int kHybHeaderBytes = 1024;
 constexpr int kHybT1Bytes = kHybNV * 128;       // one copy (hi or lo) of T1[voxel][32 taps]
 constexpr int kHybTS = kHybNV + 4;              // tap stride of the plain table (4 banks apart)
@@ -72,7 +76,7 @@ __host__ __device__ inline HybLayout hyb_layout(int C, int Dp, int stages) {
     L.halo_bytes = 9 * L.hslot * 4;
     L.msm_bytes = ((27 * kHybTS * 4) + 127) & ~127;
     L.stage_bytes = kHybCB * kHybNV * 4;
-    L.wacc_bytes = kHybKWarps * C * kHybWaccPad * 4;
+    L.wacc_bytes = kHybKUnits * C * kHybWaccPad * 4;  // one slot array per unit: its two K warps update disjoint channels
     L.total = (size_t)kHybHeaderBytes + 2 * kHybT1Bytes + L.w_bytes + L.halo_bytes + L.msm_bytes + (size_t)stages * L.stage_bytes + L.wacc_bytes;
     return L;
 }
@@ -85,7 +89,7 @@ __device__ __forceinline__ void prefetch_l2_5d(const CUtensorMap *map, int c0, i
 __global__ void __launch_bounds__(kHybThreads, 1)
 fused_backward3d_hybrid_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_gin_prefetch,
                                const __grid_constant__ CUtensorMap map_gout, const BwdParams p) {
-    constexpr int RT = 9, TAPS = 27, TX = kHybTX, TR = kHybRows, NV = kHybNV, CB = kHybCB, KH = 64, TS = kHybTS;
+    constexpr int RT = 9, TAPS = 27, TX = kHybTX, TR = kHybRows, NV = kHybNV, CB = kHybCB, KH = 32, TS = kHybTS;
     constexpr int CHAN = NV;          // floats of one channel in a ring stage
     constexpr int STAGE = CB * CHAN;  // floats of a ring stage
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -122,7 +126,7 @@ fused_backward3d_hybrid_kernel(const __grid_constant__ CUtensorMap map_in, const
     if (tid == 0) {
         for (int s = 0; s < S; ++s) {
             tma::mbar_init(&full[s], 1);
-            tma::mbar_init(&empty[s], kHybKWarps / 2);  // the K warps of one parity
+            tma::mbar_init(&empty[s], kHybKUnits);  // the K warps of one parity
         }
         tma::mbar_init(halo_full, 1);
         tma::mbar_init(halo_empty, 1);
@@ -147,7 +151,7 @@ fused_backward3d_hybrid_kernel(const __grid_constant__ CUtensorMap map_in, const
         *reinterpret_cast<float *>(wbuf + off) = hi;
         *reinterpret_cast<float *>(wbuf + L.mrows * 128 + off) = w - hi;
     }
-    for (int i = tid; i < kHybKWarps * C * kHybWaccPad; i += kHybThreads) wacc[i] = 0.f;
+    for (int i = tid; i < kHybKUnits * C * kHybWaccPad; i += kHybThreads) wacc[i] = 0.f;
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     if (warp == 0) umma::tmem_alloc(tmem_base_slot, 512);
     tma::allow_dependents();
@@ -295,14 +299,14 @@ fused_backward3d_hybrid_kernel(const __grid_constant__ CUtensorMap map_in, const
         }
     } else if (warp >= kHybKWarp0 && warp < kHybKWarp0 + kHybKWarps) {
         // ===================================== K warps =====================================
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kHybRegsMain));
-        // unit = (row, half) of the tile: 64 voxels; the warps of parity 0 / 1 take the even / odd ring
-        // stages.  lane = (qw, tl): taps tl + 8 {0..3}; voxels 4 (4 j + qw) + {0..3}, j = 0..3, of the unit.
-        const int kw = warp - kHybKWarp0, unit = kw & 3, parity = kw >> 2, r = unit >> 1, h = unit & 1;
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kHybRegsK));
+        // unit = 32 voxels of the tile (row r, columns 32 xs ..); the warps of parity 0 / 1 take the even /
+        // odd ring stages.  lane = (qw, tl): taps tl + 8 {0..3}; voxels 4 (4 j + qw) + {0..3}, j = 0..1.
+        const int kw = warp - kHybKWarp0, unit = kw & (kHybKUnits - 1), parity = kw / kHybKUnits, r = unit >> 2, xs = unit & 3;
         const int qw = lane >> 3, tl = lane & 7;
         const bool hi = (lane & 16) != 0, mid = (lane & 8) != 0;
         const int tfinal = tl + 8 * ((hi ? 2 : 0) + (mid ? 1 : 0));  // the tap whose sum this lane ends up with
-        float *wslot = wacc + (size_t)kw * C * kHybWaccPad + tfinal;
+        float *wslot = wacc + (size_t)unit * C * kHybWaccPad + tfinal;
         uint32_t tc = 0, s = 0, ph = 0;
         for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++tc) {
             split_wait(table_full, tc & 1u, abort_flag, p.status, 8);
@@ -310,9 +314,9 @@ fused_backward3d_hybrid_kernel(const __grid_constant__ CUtensorMap map_in, const
 #pragma unroll
             for (int a = 0; a < 4; ++a) {
                 const int ta = tl + 8 * a;
-                const float4 *m4 = reinterpret_cast<const float4 *>(msm + (ta < TAPS ? ta : 0) * TS + r * TX + KH * h);
+                const float4 *m4 = reinterpret_cast<const float4 *>(msm + (ta < TAPS ? ta : 0) * TS + r * TX + KH * xs);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < KH / 16; ++j) {
                     float4 q = m4[4 * j + qw];
                     if (ta >= TAPS) q = make_float4(0.f, 0.f, 0.f, 0.f);
                     Mk[a][2 * j] = make_float2(q.x, q.y), Mk[a][2 * j + 1] = make_float2(q.z, q.w);
@@ -323,23 +327,23 @@ fused_backward3d_hybrid_kernel(const __grid_constant__ CUtensorMap map_in, const
             for (int g = 0; g < ngroups; ++g) {
                 if ((g & 1) == parity) {
                     split_wait(&full[s], ph, abort_flag, p.status, 2);
-                    const float4 *ain0 = reinterpret_cast<const float4 *>(ring + (size_t)s * STAGE + r * TX + KH * h) + qw;
+                    const float4 *ain0 = reinterpret_cast<const float4 *>(ring + (size_t)s * STAGE + r * TX + KH * xs) + qw;
                     float tot[CB];
 #pragma unroll
                     for (int cp = 0; cp < CB; cp += 2) {
                         const float4 *ain = ain0 + cp * (CHAN / 4);
-                        float4 av[2][4];
+                        float4 av[2][KH / 16];
 #pragma unroll
                         for (int u = 0; u < 2; ++u)
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) av[u][j] = ain[u * (CHAN / 4) + 4 * j];
+                            for (int j = 0; j < KH / 16; ++j) av[u][j] = ain[u * (CHAN / 4) + 4 * j];
                         float2 acc[2][4];
 #pragma unroll
                         for (int u = 0; u < 2; ++u)
 #pragma unroll
                             for (int a = 0; a < 4; ++a) acc[u][a] = make_float2(0.f, 0.f);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
+                        for (int j = 0; j < KH / 16; ++j)
 #pragma unroll
                             for (int a = 0; a < 4; ++a)
 #pragma unroll
@@ -371,7 +375,7 @@ fused_backward3d_hybrid_kernel(const __grid_constant__ CUtensorMap map_in, const
         }
     } else if (warp < kHybEpilogueWarps) {
         // ------------------------------------ epilogue warps ------------------------------------
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kHybRegsMain));
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kHybRegsEpilogue));
         // thread = channel.  M = 64: channel c sits in lane 32 (c / 16) + (c % 16) of the accumulator
         // (the upper half of each warp's lanes holds nothing); M = 128: in lane c.
         const int ch = L.mrows == 64 ? ((lane < 16) ? 16 * warp + lane : -1) : 32 * warp + lane;
@@ -386,7 +390,7 @@ fused_backward3d_hybrid_kernel(const __grid_constant__ CUtensorMap map_in, const
             const float *ibase = p.in + n * p.in_sn + (int64_t)cc * p.in_sc + z * p.in_sz + (int64_t)y0 * p.in_sy + x0;
             const bool gate_here = has_channel && ch == p.mask_channel;
             // 16 steps of 16 voxels; the gradients of three steps are in flight ahead of the sums
-            constexpr int STEPS = NV / 16, AHEAD = 4;
+            constexpr int STEPS = NV / 16, AHEAD = 2;
             float4 g[AHEAD][4];
             auto row_ok = [&](int q) { return has_channel && (y0 + (q * 16) / TX) < p.Y; };
             auto goff = [&](int q) { return (int64_t)((q * 16) / TX) * p.gi_sy + (q * 16) % TX; };
@@ -451,7 +455,7 @@ fused_backward3d_hybrid_kernel(const __grid_constant__ CUtensorMap map_in, const
             const int c = i / TAPS, t = i - c * TAPS;
             float s_ = 0.f;
 #pragma unroll
-            for (int w = 0; w < kHybKWarps; ++w) s_ += wacc[((size_t)w * C + c) * kHybWaccPad + t];
+            for (int w = 0; w < kHybKUnits; ++w) s_ += wacc[((size_t)w * C + c) * kHybWaccPad + t];
             dst[i] = s_;
         }
     }

@@ -36,7 +36,7 @@ static int launch3d_hybrid(const CUtensorMap *m, const BwdParams &p, int grid, s
     if (pool_ok < 0) {
         cudaFuncAttributes fa;
         MSD_CUDA_TRY(cudaFuncGetAttributes(&fa, kern));
-        pool_ok = (fa.numRegs * kHybThreads >= 3 * 128 * kHybRegsMain + 128 * kHybRegsProducer + 128 * kHybRegsBuilder) ? 1 : 0;
+        pool_ok = (fa.numRegs * kHybThreads >= kHybRegBudget) ? 1 : 0;
     }
     if (!pool_ok) MSD_FAIL(MSD_ERR_UNSUPPORTED, "tensor-core 3D backward: this build's register allocation does not fit its warpgroup budgets");
     MSD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
