@@ -23,8 +23,12 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 NAME = "msd_custom_convolutions_ref"
-# where the reference checkout is expected when no path is given
-DEFAULT_REF_ROOT = os.path.join(os.sep, "root", "reference")
+
+
+def default_ref_root():
+    """The reference checkout: ``$MSD_REFERENCE_ROOT``, else a directory ``reference`` beside
+    this repository."""
+    return os.environ.get("MSD_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 SOURCES = [
     "msd_pytorch/msd_custom_convolutions.cpp",
@@ -47,7 +51,7 @@ def built_path():
 
 
 def build(ref_root=None, verbose=False):
-    ref_root = ref_root or os.environ.get("MSD_REFERENCE_ROOT", DEFAULT_REF_ROOT)
+    ref_root = ref_root or default_ref_root()
     if not os.path.isdir(ref_root):
         return built_path()
     os.makedirs(OUT, exist_ok=True)
