@@ -455,3 +455,54 @@ def test_block_gradcheck_reference_configuration(cuda_device, seed):
     for i, e in enumerate(gws_o):
         assert_close(getattr(net, "weight%d" % i).grad, e, 1e-10, "grad_weight%d" % i)
     assert torch.autograd.gradcheck(net, (x.detach().clone().requires_grad_(True),), atol=1e-5, rtol=1e-3, nondet_tol=1e-9)
+
+
+def test_inference_forward_keeps_nothing(cuda_device):
+    """Inference (``model.net(x)`` under ``no_grad``, examples/getting_started.py:160-175 of the
+    reference): same output as the training forward, and the dense channel buffer is released
+    as soon as the output exists (nothing is saved for a backward pass)."""
+    from msd_pytorch_b200 import MSDRegressionModel
+
+    dev = cuda_device
+    torch.manual_seed(5)
+    model = MSDRegressionModel(1, 1, 20, 1, ndim=2)
+    for p in model.msd.parameters():
+        p.data.normal_(0, 0.2)
+    x = torch.randn(2, 1, 256, 256, device=dev)
+    y_train = model.net(x)
+    torch.cuda.synchronize()
+    held = torch.cuda.memory_allocated(dev)
+    del y_train
+    torch.cuda.synchronize()
+    base = torch.cuda.memory_allocated(dev)
+    with torch.no_grad():
+        y = model.net(x)
+    torch.cuda.synchronize()
+    after = torch.cuda.memory_allocated(dev)
+    buffer_bytes = 2 * 21 * 256 * 256 * 4
+    assert held - base >= buffer_bytes, "the training forward keeps the channel buffer for its backward"
+    assert after - base < buffer_bytes // 4, "the inference forward must not keep the channel buffer"
+    y2 = model.net(x)
+    assert torch.equal(y, y2.detach())
+
+
+def test_data_parallel_two_gpus(cuda_device):
+    """``parallel=True`` (nn.DataParallel, msd_regression_model.py:78-79 of the reference) on two
+    GPUs: the ops are called from one host thread per GPU on tensors of that GPU; the result
+    equals the single-GPU model with the same parameters."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from msd_pytorch_b200 import MSDRegressionModel
+
+    torch.manual_seed(6)
+    single = MSDRegressionModel(1, 2, 8, 1, ndim=2)
+    for p in single.msd.parameters():
+        p.data.normal_(0, 0.2)
+    multi = MSDRegressionModel(1, 2, 8, 1, ndim=2, parallel=True)
+    multi.net.module.load_state_dict(single.net.state_dict())
+    x, t = torch.randn(4, 1, 64, 96), torch.randn(4, 2, 64, 96)
+    l1 = single.forward(x, t)
+    l2 = multi.forward(x, t)
+    assert abs(l1 - l2) <= 1e-5 * abs(l1)
+    assert_close(multi.output, single.output, 1e-5, "DataParallel output")
+    multi.learn(x, t)
