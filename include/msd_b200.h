@@ -173,6 +173,24 @@ MSD_API int msd_final_backward(int dtype, const msd_tensor_t *result, const msd_
                        void *workspace, size_t workspace_bytes, int device, void *stream);
 MSD_API size_t msd_final_workspace_bytes(int64_t c_in, int64_t c_out);
 
+/* No counterpart in the reference: what msd_block_backward WOULD do, layer by layer, decided
+ * on the host alone (no GPU is touched, data pointers are only inspected for alignment).
+ * `codes_out[i]` (i = layer, `depth` <= 64 entries) is a combination of
+ *   MSD_PLAN_TUNED                the fused tuned kernel runs (otherwise the generic kernels)
+ *   MSD_PLAN_GATES_TOP_IN_PLACE   topmost layer: its gradient channel is gated in place first
+ *   MSD_PLAN_READS_GATED          the layer receives its gradient channel already gated
+ *   MSD_PLAN_GATES_CHANNEL_BELOW  the layer stores the gradient of the channel below gated
+ * A layer gates the channel below only when the layer below runs a tuned kernel too; a gated
+ * gradient never meets a kernel that would gate it again.  `wants_grad_weight` (per layer,
+ * NULL = all) says for which layers a weight gradient is requested. */
+#define MSD_PLAN_TUNED 1
+#define MSD_PLAN_GATES_TOP_IN_PLACE 2
+#define MSD_PLAN_READS_GATED 4
+#define MSD_PLAN_GATES_CHANNEL_BELOW 8
+MSD_API int msd_block_backward_plan(int dtype, const msd_tensor_t *result, const msd_tensor_t *gradients, int c_in,
+                            int depth, int width, const int *dilations, const unsigned char *wants_grad_weight,
+                            size_t workspace_bytes, int *codes_out);
+
 /* ---- z-slab decomposition of one 3D volume over several GPUs ---- */
 
 /* No counterpart in the reference (it has no spatial decomposition).  One layer of the

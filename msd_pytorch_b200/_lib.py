@@ -56,6 +56,7 @@ def _load():
         "msd_block_forward": (i, [i, T, i, i, i, ctypes.POINTER(vp), vp, ctypes.POINTER(i), vp, sz, i, vp]),
         "msd_block_backward": (i, [i, T, T, i, i, i, ctypes.POINTER(vp), ctypes.POINTER(i), ctypes.POINTER(vp), vp, vp, sz, i, vp]),
         "msd_block_workspace_bytes": (sz, [i, i, i64, i, i, i]),
+        "msd_block_backward_plan": (i, [i, T, T, i, i, i, ctypes.POINTER(i), ctypes.c_char_p, sz, ctypes.POINTER(i)]),
         "msd_final_forward": (i, [i, T, vp, vp, T, i, vp]),
         "msd_final_backward": (i, [i, T, T, vp, T, vp, vp, vp, sz, i, vp]),
         "msd_final_workspace_bytes": (sz, [i64, i64]),
@@ -86,7 +87,7 @@ EXPORTED = [
     "msd_version", "msd_last_error_string", "msd_workspace_bytes", "msd_forward_workspace_bytes",
     "msd_conv_forward", "msd_conv_relu_forward", "msd_conv_backward_x", "msd_conv_relu_backward_x",
     "msd_conv_backward_k", "msd_conv_relu_backward_k", "msd_conv_backward_bias", "msd_conv_relu_backward_bias",
-    "msd_block_forward", "msd_block_backward", "msd_block_workspace_bytes",
+    "msd_block_forward", "msd_block_backward", "msd_block_workspace_bytes", "msd_block_backward_plan",
     "msd_slab_layer_forward", "msd_slab_layer_backward",
     "msd_final_forward", "msd_final_backward", "msd_final_workspace_bytes",
     "msd_tuning_num_variants", "msd_tuning_set", "msd_tuning_get",

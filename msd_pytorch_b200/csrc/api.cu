@@ -263,6 +263,76 @@ size_t msd_block_workspace_bytes(int dtype, int ndim, int64_t voxels, int c_in, 
     return all > one ? all : one;
 }
 
+// What one layer of a block backward will do; decided on the host from shapes, pointers'
+// alignment, dilations and the launch table alone, so that it can be checked without a GPU.
+struct LayerDecision {
+    bool tuned;        // the fused tuned kernel runs (else the three generic kernels)
+    bool gate_first;   // topmost layer: its gradient channel is gated in place before the kernel runs
+    bool reads_gated;  // the gradient channel arrives already multiplied by the layer's ReLU gate
+    bool gates_below;  // the kernel stores the gradient of channel n_i - 1 multiplied by THAT layer's gate
+};
+
+namespace {
+struct BlockBackwardPlanner {
+    int dtype, nd, c_in, depth, width;
+    View r, gr;
+    const void *const *weights;
+    const int *dilations;
+    void *const *grad_weights;           // real call: the pointers; plan call: null, see wants_gw
+    const unsigned char *wants_gw;       // plan call: per layer, non-zero = weight gradient wanted (null: all wanted)
+    bool plan_only;
+    void *grad_bias;
+    void *workspace;
+    size_t workspace_bytes;
+    fast::ReduceList *pending;
+    size_t es() const { return dtype == MSD_F64 ? 8 : 4; }
+    bool fast_dtype() const { return dtype == MSD_F32 && width == 1; }
+    void *gk_of(int i) const {
+        if (plan_only) return (!wants_gw || wants_gw[i]) ? (void *)(uintptr_t)256 : nullptr;
+        return grad_weights ? grad_weights[i] : nullptr;
+    }
+    fast::BackwardArgs layer_args(int i, View *out, View *gout, View *in, View *gin) const {
+        const int64_t n_i = c_in + (int64_t)i * width;
+        *out = channel_slice(r, n_i, width, es());
+        *in = channel_slice(r, 0, n_i, es());
+        *gout = channel_slice(gr, n_i, width, es());
+        *gin = channel_slice(gr, 0, n_i, es());
+        const float *k = plan_only ? (const float *)(uintptr_t)256 : (const float *)weights[i];
+        return fast::BackwardArgs{out, gout, in, gin, k, (float *)gk_of(i), grad_bias ? (float *)grad_bias + i : nullptr, nd, dilations[i],
+                                  workspace, workspace_bytes, pending, -1};
+    }
+    // `gated`: the gradient channel layer i reads is already multiplied by its ReLU gate (done by
+    // the kernel of the layer above when it stored that channel).  A layer hands its gradient over
+    // gated only when the layer below will run the tuned kernel as well, judged one layer ahead
+    // with that layer's own arguments.
+    LayerDecision decide(int i, bool gated, fast::BackwardArgs *a, View *out, View *gout, View *in, View *gin) const {
+        LayerDecision dec{false, false, gated, false};
+        if (!fast_dtype()) {
+            *out = channel_slice(r, c_in + (int64_t)i * width, width, es()), *in = channel_slice(r, 0, c_in + (int64_t)i * width, es());
+            *gout = channel_slice(gr, c_in + (int64_t)i * width, width, es()), *gin = channel_slice(gr, 0, c_in + (int64_t)i * width, es());
+            return dec;
+        }
+        *a = layer_args(i, out, gout, in, gin);
+        // the topmost gradient channel can be gated in place before the first layer runs
+        dec.gate_first = !gated && i == depth - 1 && fast::gate_channel_supported(*gout, *out);
+        if (gated || dec.gate_first) a->out = nullptr;  // eligibility is judged with the halo buffers this launch will really use
+        dec.tuned = fast::backward_supported(*a);
+        if (!dec.tuned) {
+            dec.gate_first = false;
+            return dec;
+        }
+        if (a->gk != nullptr && i > 0) {
+            View o2, go2, in2, gi2;
+            fast::BackwardArgs below = layer_args(i - 1, &o2, &go2, &in2, &gi2);
+            below.out = nullptr;  // what that layer would be given after a gated hand-over
+            dec.gates_below = fast::backward_supported(below);
+        }
+        a->mask_channel = dec.gates_below ? (int)(c_in + (int64_t)i * width - 1) : -1;
+        return dec;
+    }
+};
+}  // namespace
+
 int msd_block_backward(int dtype, const msd_tensor_t *result, const msd_tensor_t *gradients, int c_in, int depth, int width,
                        const void *const *weights, const int *dilations, void *const *grad_weights, void *grad_bias, void *workspace,
                        size_t workspace_bytes, int device, void *stream) {
@@ -276,63 +346,30 @@ int msd_block_backward(int dtype, const msd_tensor_t *result, const msd_tensor_t
     DeviceGuard g(device);
     MSD_CUDA_TRY(g.status);
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t es = dtype == MSD_F64 ? 8 : 4;
     fast::ReduceList pending;
     pending.count = 0, pending.ws_used = 0;
-    // `gated`: the gradient channel the next layer reads is already multiplied by that layer's
-    // ReLU gate (done by the kernel of the layer above when it stores that channel), so the
-    // layer's kernel needs no halo of the activation.  The topmost channel is gated up front.
-    // A layer hands its gradient over gated only when the layer below will run the tuned
-    // kernel as well (checked one layer ahead, with that layer's own arguments).
+    const BlockBackwardPlanner P{dtype, nd, c_in, depth, width, r, gr, weights, dilations, grad_weights, nullptr, false, grad_bias, workspace, workspace_bytes, &pending};
+    const size_t es = P.es();
     bool gated = false;
-    const bool fast_dtype = dtype == MSD_F32 && width == 1;
     tma::OverlapScope overlap;  // see msd_block_forward
-    auto layer_args = [&](int i, View *out, View *gout, View *in, View *gin) {
-        const int64_t n_i = c_in + (int64_t)i * width;
-        *out = channel_slice(r, n_i, width, es);
-        *in = channel_slice(r, 0, n_i, es);
-        *gout = channel_slice(gr, n_i, width, es);
-        *gin = channel_slice(gr, 0, n_i, es);
-        return fast::BackwardArgs{out, gout, in, gin, (const float *)weights[i], grad_weights ? (float *)grad_weights[i] : nullptr,
-                                  grad_bias ? (float *)grad_bias + i : nullptr, nd, dilations[i], workspace, workspace_bytes, &pending, -1};
-    };
     for (int i = depth - 1; i >= 0; --i) {
-        const int64_t n_i = c_in + (int64_t)i * width;
         View out, gout, in, gin;
+        fast::BackwardArgs a{};
+        const LayerDecision dec = P.decide(i, gated, &a, &out, &gout, &in, &gin);
         const int d = dilations[i];
         void *gk = grad_weights ? grad_weights[i] : nullptr;
         void *gb = grad_bias ? (char *)grad_bias + (size_t)i * width * es : nullptr;
-        if (fast_dtype) {
-            fast::BackwardArgs a = layer_args(i, &out, &gout, &in, &gin);
-            // the topmost gradient channel can be gated in place before the first layer runs
-            const bool gate_first = !gated && i == depth - 1 && fast::gate_channel_supported(gout, out);
-            if (gated || gate_first) a.out = nullptr;  // eligibility is judged with the halo buffers this launch will really use
-            if (fast::backward_supported(a)) {
-                bool can_gate_next = false;
-                if (gk != nullptr && i > 0) {
-                    View o2, go2, in2, gi2;
-                    fast::BackwardArgs below = layer_args(i - 1, &o2, &go2, &in2, &gi2);
-                    below.out = nullptr;  // what that layer would be given after a gated hand-over
-                    can_gate_next = fast::backward_supported(below);
-                }
-                a.mask_channel = can_gate_next ? (int)(n_i - 1) : -1;
-                if (gate_first) {
-                    if ((rc = fast::gate_channel(gout, out, device, s))) return rc;
-                    gated = true;
-                }
-                if ((rc = fast::backward(a, device, s))) return rc;
-                tma::set_overlap_allowed(true);
-                gated = can_gate_next;
-                continue;
-            }
-        } else {
-            out = channel_slice(r, n_i, width, es), in = channel_slice(r, 0, n_i, es);
-            gout = channel_slice(gr, n_i, width, es), gin = channel_slice(gr, 0, n_i, es);
+        if (dec.tuned) {
+            if (dec.gate_first && (rc = fast::gate_channel(gout, out, device, s))) return rc;
+            if ((rc = fast::backward(a, device, s))) return rc;
+            tma::set_overlap_allowed(true);
+            gated = dec.gates_below;
+            continue;
         }
         // the generic kernels use the workspace from its start: finish pending reductions first
         if ((rc = fast::flush_reductions(&pending, s))) return rc;
         // A gradient that arrived already gated must not be gated again from `out`; the look-ahead
-        // above keeps this from happening, the un-gated kernels are the safe answer if it ever does.
+        // keeps this from happening, the un-gated kernels are the safe answer if it ever does.
         const bool relu = !gated;
         const View *gate = relu ? &out : nullptr;
         if ((rc = generic::backward_x(dtype, relu, gate, gout, weights[i], gin, nd, d, s))) return rc;
@@ -342,6 +379,35 @@ int msd_block_backward(int dtype, const msd_tensor_t *result, const msd_tensor_t
         gated = false;
     }
     return fast::flush_reductions(&pending, s);
+}
+
+int msd_block_backward_plan(int dtype, const msd_tensor_t *result, const msd_tensor_t *gradients, int c_in, int depth, int width,
+                            const int *dilations, const unsigned char *wants_grad_weight, size_t workspace_bytes, int *codes_out) {
+    View r, gr;
+    int nd, nd2;
+    if (!codes_out) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "msd_block_backward_plan: codes_out is null");
+    const void *dummy = (const void *)(uintptr_t)256;
+    // block_checks wants a weight pointer per layer; the plan needs none
+    const void *stack_ptrs[64];
+    const void **ptrs = stack_ptrs;
+    if (depth > 64) MSD_FAIL(MSD_ERR_LIMIT, "msd_block_backward_plan: at most 64 layers per query");
+    for (int i = 0; i < depth; ++i) ptrs[i] = dummy;
+    int rc = block_checks("msd_block_backward_plan", dtype, result, c_in, depth, width, ptrs, dilations, &r, &nd);
+    if (rc) return rc;
+    if ((rc = views2("msd_block_backward_plan", result, gradients, &r, &gr, &nd2))) return rc;
+    if (gr.c != r.c) MSD_FAIL(MSD_ERR_BAD_ARGUMENT, "msd_block_backward_plan: gradients and result differ in channels");
+    const BlockBackwardPlanner P{dtype, nd, c_in, depth, width, r, gr, nullptr, dilations, nullptr, wants_grad_weight, true, (void *)(uintptr_t)256,
+                                 (void *)(uintptr_t)256, workspace_bytes, nullptr};
+    bool gated = false;
+    for (int i = depth - 1; i >= 0; --i) {
+        View out, gout, in, gin;
+        fast::BackwardArgs a{};
+        const LayerDecision dec = P.decide(i, gated, &a, &out, &gout, &in, &gin);
+        codes_out[i] = (dec.tuned ? MSD_PLAN_TUNED : 0) | (dec.gate_first ? MSD_PLAN_GATES_TOP_IN_PLACE : 0) |
+                       (dec.reads_gated ? MSD_PLAN_READS_GATED : 0) | (dec.tuned && dec.gates_below ? MSD_PLAN_GATES_CHANNEL_BELOW : 0);
+        gated = dec.tuned ? dec.gates_below : false;
+    }
+    return MSD_OK;
 }
 
 // One layer of a block on a z-slab: same kernels as the block entry points, restricted to the

@@ -42,6 +42,7 @@ namespace fast {
 constexpr int kSplitRows = 4;
 constexpr int kSplitTX = 128;
 constexpr int kSplitCB = 4;                                       // channels per ring stage
+constexpr int kSplitKU = 4;                                       // channels a K warp processes per loop iteration
 constexpr int kSplitKHalf = 64;                                   // voxels per K warp
 constexpr int kSplitXWarps = kSplitRows;
 constexpr int kSplitKWarps = 2 * kSplitRows;
@@ -305,35 +306,35 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
                 split_wait(&full[s], ph, abort_flag, p.status, 2);
                 const float4 *ain0 = reinterpret_cast<const float4 *>(ring + s * STAGE + r * TX + KH * h) + qw;  // in[g * CB], this half row
                 float tot[CB];
-                // two channels at a time: eight independent chains of packed FMAs, and one
-                // reduce-scatter over the four quarter-warps (fixed tree) for both of them, so
-                // that its two shuffle rounds are paid once per pair.  Channels past C read a
-                // zero-filled stage.
+                // kSplitKU channels at a time: 4 kSplitKU independent chains of packed FMAs, and one
+                // reduce-scatter over the four quarter-warps (fixed tree) for all of them, so that its
+                // two shuffle rounds are paid once per group.  The activations are loaded one 16-voxel
+                // slice at a time.  Channels past C read a zero-filled stage.
 #pragma unroll
-                for (int cp = 0; cp < CB; cp += 2) {
+                for (int cp = 0; cp < CB; cp += kSplitKU) {
                     const float4 *ain = ain0 + cp * (CHAN / 4);
-                    float4 av[2][4];
+                    float2 acc[kSplitKU][4];
 #pragma unroll
-                    for (int u = 0; u < 2; ++u)
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) av[u][j] = ain[u * (CHAN / 4) + 4 * j];  // one 64-byte run per warp and load
-                    float2 acc[2][4];
-#pragma unroll
-                    for (int u = 0; u < 2; ++u)
+                    for (int u = 0; u < kSplitKU; ++u)
 #pragma unroll
                         for (int a = 0; a < 4; ++a) acc[u][a] = make_float2(0.f, 0.f);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
+                    for (int j = 0; j < 4; ++j) {
+                        float4 av[kSplitKU];
+#pragma unroll
+                        for (int u = 0; u < kSplitKU; ++u) av[u] = ain[u * (CHAN / 4) + 4 * j];  // one 64-byte run per warp and load
 #pragma unroll
                         for (int a = 0; a < 4; ++a)
 #pragma unroll
-                            for (int u = 0; u < 2; ++u) {
-                                acc[u][a] = __ffma2_rn(make_float2(av[u][j].x, av[u][j].y), Mk[a][2 * j], acc[u][a]);
-                                acc[u][a] = __ffma2_rn(make_float2(av[u][j].z, av[u][j].w), Mk[a][2 * j + 1], acc[u][a]);
-                            }
-                    float k0[2], k1[2];
+                            for (int u = 0; u < kSplitKU; ++u) acc[u][a] = __ffma2_rn(make_float2(av[u].x, av[u].y), Mk[a][2 * j], acc[u][a]);
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
+                        for (int a = 0; a < 4; ++a)
+#pragma unroll
+                            for (int u = 0; u < kSplitKU; ++u) acc[u][a] = __ffma2_rn(make_float2(av[u].z, av[u].w), Mk[a][2 * j + 1], acc[u][a]);
+                    }
+                    float k0[kSplitKU], k1[kSplitKU];
+#pragma unroll
+                    for (int u = 0; u < kSplitKU; ++u) {
                         // sums over the lane's 16 voxels; the lane keeps taps {2 hi, 2 hi + 1} of its four
                         const float s0 = acc[u][0].x + acc[u][0].y, s1 = acc[u][1].x + acc[u][1].y;
                         const float s2 = acc[u][2].x + acc[u][2].y, s3 = acc[u][3].x + acc[u][3].y;
@@ -341,7 +342,7 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
                         k1[u] = (hi ? s3 : s1) + __shfl_xor_sync(0xffffffffu, hi ? s1 : s3, 16);
                     }
 #pragma unroll
-                    for (int u = 0; u < 2; ++u)  // ... then tap 2 hi + mid
+                    for (int u = 0; u < kSplitKU; ++u)  // ... then tap 2 hi + mid
                         tot[cp + u] = (mid ? k1[u] : k0[u]) + __shfl_xor_sync(0xffffffffu, mid ? k0[u] : k1[u], 8);
                 }
                 __syncwarp();

@@ -105,3 +105,47 @@ def test_noalloc_limit_boundaries_need_no_gpu():
         assert b"built-in array" in L.msd_last_error_string()
         x = _desc((1, c_ok) + shape[2:])
         assert L.msd_conv_relu_backward_k_noalloc(0, y, y, x, 256, 1, 0, None) != 5  # accepted as far as the limit goes (no GPU here)
+
+
+def _plan(shape, c_in, dilations, dtype=0, wants=None, ws_bytes=64 << 20):
+    from msd_pytorch_b200 import _lib
+
+    L = _lib.lib
+    depth = len(dilations)
+    full = (shape[0], c_in + depth) + tuple(shape[1:])
+    res, grad = _desc(full, ptr=1 << 20), _desc(full, ptr=1 << 30)
+    dil = (ctypes.c_int * depth)(*dilations)
+    codes = (ctypes.c_int * depth)()
+    w = None if wants is None else bytes(wants)
+    rc = L.msd_block_backward_plan(dtype, res, grad, c_in, depth, 1, dil, w, ws_bytes, codes)
+    assert rc == 0, L.msd_last_error_string()
+    return list(codes)
+
+
+def test_block_backward_plan_mixes_tuned_and_generic_layers():
+    """The layer-by-layer decisions of msd_block_backward, made on the host alone: a layer hands
+    its gradient over gated only when the layer below runs a tuned kernel too, so a gated
+    gradient never meets a kernel that would gate it again (dilations beyond the tuned range sit
+    above, below and between tuned layers)."""
+    TUNED, TOP, READS, BELOW = 1, 2, 4, 8
+    # power-of-two dilations up to 32 on a 64 x 96 image: the top layer (d = 32) is generic
+    assert _plan((2, 64, 96), 1, [1, 2, 4, 8, 16, 32]) == [TUNED | READS, TUNED | READS | BELOW, TUNED | READS | BELOW, TUNED | READS | BELOW, TUNED | BELOW, 0]
+    # an untuned layer BELOW a tuned one: the tuned one must not gate for it
+    assert _plan((2, 48, 64), 1, [20, 1]) == [0, TUNED | TOP]
+    # ... and between two tuned ones
+    assert _plan((2, 48, 64), 1, [1, 20, 2]) == [TUNED, 0, TUNED | TOP]
+    # the same in 3D
+    assert _plan((1, 24, 24, 32), 1, [2, 20, 1, 3]) == [TUNED, 0, TUNED | READS, TUNED | TOP | BELOW]
+    # everything tuned: the top channel is gated in place, every other one by the layer above
+    assert _plan((1, 32, 64), 1, [1, 2, 3, 4]) == [TUNED | READS, TUNED | READS | BELOW, TUNED | READS | BELOW, TUNED | TOP | BELOW]
+    # float64 takes the generic kernels throughout
+    assert _plan((1, 32, 64), 1, [1, 2, 3], dtype=1) == [0, 0, 0]
+    # a layer whose weight gradient is not wanted runs the input-gradient-only kernel, which cannot gate
+    assert _plan((1, 32, 64), 1, [1, 2, 3, 4], wants=[1, 1, 0, 1]) == [TUNED | READS, TUNED | BELOW, TUNED | READS, TUNED | TOP | BELOW]
+    # every state is consistent: READS on layer i  <=>  BELOW on layer i + 1 (or TOP on the top layer never implies READS)
+    for dil in ([1, 2, 4, 8, 16, 32], [20, 1], [1, 20, 2], [3, 17, 5, 18, 7], [1] * 12):
+        codes = _plan((2, 64, 96), 1, dil)
+        for i in range(len(dil) - 1):
+            assert bool(codes[i] & READS) == bool(codes[i + 1] & BELOW), (dil, codes)
+            if codes[i] & READS:
+                assert codes[i] & TUNED, "a gated gradient must only reach a tuned layer"
