@@ -42,7 +42,7 @@ namespace fast {
 constexpr int kSplitRows = 4;
 constexpr int kSplitTX = 128;
 constexpr int kSplitCB = 4;                                       // channels per ring stage
-constexpr int kSplitKU = 4;                                       // channels a K warp processes per loop iteration
+constexpr int kSplitKU = 2;                                       // channels a K warp processes per loop iteration (4: measured 4 % slower)
 constexpr int kSplitKHalf = 64;                                   // voxels per K warp
 constexpr int kSplitXWarps = kSplitRows;
 constexpr int kSplitKWarps = 2 * kSplitRows;
