@@ -63,12 +63,12 @@ def algorithmic_bytes(depth, voxels):
 
 
 # DRAM traffic per launch measured by ncu (dram__bytes_read.sum + dram__bytes_write.sum) divided
-# by the algorithmic bytes of the captured launch: 2D backward 1224.7 / 1275.1 MB and 2D forward
-# 429.6 / 427.8 MB (batch 8 of 512x512, 50 input channels, dilation 10); 3D backward
-# 2495.1 / 2550.1 MB (batch 2 of 128^3, 50 input channels, dilation 2) and 3D forward
-# 509.6 / 436.2 MB (batch 2 of 128^3, 25 input channels, dilation 4).  Traffic grows with the channel count like the algorithmic bytes do, so the ratio
-# is applied to the average launch.
-NCU_TRAFFIC_RATIO = {("bwd", 2): 1224.7 / 1275.1, ("fwd", 2): 429.6 / 427.8, ("bwd", 3): 2495.1 / 2550.1, ("fwd", 3): 509.6 / 436.2}
+# by the algorithmic bytes of the captured launch (`--one-layer` captures summarised in profiles/):
+# 2D backward 1224.3 / 1275.1 MB and 2D forward 436.0 / 427.8 MB (c2:50:10); 3D backward
+# 2494.3 / 2550.1 MB (c4:50:2) and 3D forward 512.0 / 436.2 MB (c4:25:4, both forward kernels).
+# Traffic grows with the channel count like the algorithmic bytes do, so the ratio is applied to
+# the average launch.
+NCU_TRAFFIC_RATIO = {("bwd", 2): 1224.3 / 1275.1, ("fwd", 2): 436.0 / 427.8, ("bwd", 3): 2494.3 / 2550.1, ("fwd", 3): 512.0 / 436.2}
 
 
 def measured_peak():

@@ -23,7 +23,8 @@
 // Data movement.  One ring stage holds kSplitCB consecutive channels of the tile: two TMA
 // boxes (activations, gradients) of kSplitCB x 4 x 128 floats, so that the cost of issuing a
 // copy and of the full/empty hand-shake is paid once per kSplitCB channels.  The 9 halo row
-// groups of gout (and of out, for the ReLU gate) land by TMA.  The builder warps turn them into
+// groups of gout (and of out, for the ReLU gate) land by TMA in one of two buffers (tiles
+// alternate), requested a whole tile ahead.  The builder warps turn them into
 // the table  Msm[t][row][x] = M_t(voxel)  in two short passes (gate + y/z folds in place; x
 // shifts + x folds into the table) while the consumers are still streaming the channels of
 // the previous tile; both kinds of consumer warps then fill their registers from the table
@@ -153,19 +154,19 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw);
     uint64_t *empty = full + kSplitMaxStages;
-    uint64_t *halo_full = empty + kSplitMaxStages;  // the halo rows of a tile have landed
-    uint64_t *halo_empty = halo_full + 1;           // ... have been turned into the table: the slots are free
-    uint64_t *m_done = halo_empty + 1;              // every consumer warp has its M registers: the table is free
+    uint64_t *halo_full = empty + kSplitMaxStages;  // [2] the halo rows of a tile have landed (two buffers, tiles alternate)
+    uint64_t *halo_empty = halo_full + 2;           // [2] ... have been turned into the table: the slots are free
+    uint64_t *m_done = halo_empty + 2;              // every consumer warp has its M registers: the table is free
     uint64_t *table_full = m_done + 1;              // the table of a tile is complete
     volatile int *abort_flag = reinterpret_cast<volatile int *>(table_full + 1);
     float *red = reinterpret_cast<float *>(smem_raw + 384);
     const int TXP = TX + 2 * p.Dp;
     const bool gate = p.out != nullptr;
-    float *rows = reinterpret_cast<float *>(smem_raw + kSplitHeaderBytes);
+    float *rows0 = reinterpret_cast<float *>(smem_raw + kSplitHeaderBytes);
     const int HSLOT = (TR * TXP + 31) & ~31;
     constexpr int TS = TR * TX + 4;  // tap stride of the table: 4 banks apart
-    float *orows = rows + RT * HSLOT;
-    float *msm = orows + (gate ? RT * HSLOT : 0);
+    const int HBUF = RT * HSLOT * (gate ? 2 : 1);  // floats of one halo buffer: rows of gout, then (with a gate) rows of out
+    float *msm = rows0 + 2 * HBUF;
     float *ring = msm + ((TAPS * TS + 31) & ~31);
     float *wsm = ring + (size_t)p.stages * STAGE;
     float *wacc = wsm + p.C * kSplitWPad;
@@ -179,8 +180,10 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
             tma::mbar_init(&full[s], 1);
             tma::mbar_init(&empty[s], kSplitConsumerWarps);
         }
-        tma::mbar_init(halo_full, 1);
-        tma::mbar_init(halo_empty, 1);
+        for (int b = 0; b < 2; ++b) {
+            tma::mbar_init(&halo_full[b], 1);
+            tma::mbar_init(&halo_empty[b], 1);
+        }
         tma::mbar_init(m_done, kSplitConsumerWarps);
         tma::mbar_init(table_full, 1);
         *abort_flag = 0;
@@ -206,23 +209,27 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
             tma::prefetch_tensormap(&map_gout);
             if (gate) tma::prefetch_tensormap(&map_out);
             const uint32_t halo_bytes = (uint32_t)(RT * TR * TXP * 4) * (gate ? 2u : 1u);
-            auto issue_halo = [&](long long tile) {
+            // Halo rows of the block's `use`-th tile go to buffer use & 1; a buffer is free again once the
+            // builders have turned its previous content (tile use - 2) into the table.
+            auto issue_halo = [&](long long tile, uint32_t use) {
                 const int tx_i = (int)(tile % p.tiles_x);
                 const int ty_i = (int)((tile / p.tiles_x) % p.tiles_y);
                 const long long nz = tile / tiles_per_plane;
                 const int z = p.z0 + (int)(nz % p.ZW), n = (int)(nz / p.ZW);
                 const int bx = tx_i * TX - p.Dp, y0 = ty_i * TR;
-                tma::mbar_arrive_expect_tx(halo_full, halo_bytes);
+                const int b = use & 1;
+                float *rows = rows0 + b * HBUF, *orows = rows + RT * HSLOT;
+                if (use >= 2) split_wait(&halo_empty[b], ((use >> 1) & 1u) ^ 1u, abort_flag, p.status, 5);
+                tma::mbar_arrive_expect_tx(&halo_full[b], halo_bytes);
 #pragma unroll 1
                 for (int rt = 0; rt < RT; ++rt) {
                     const int by = y0 + p.d * (1 - rt % 3), bz = z + p.d * (1 - rt / 3);
-                    tma::tensor_g2s_5d(rows + rt * HSLOT, &map_gout, bx, by, bz, 0, n, halo_full);
-                    if (gate) tma::tensor_g2s_5d(orows + rt * HSLOT, &map_out, bx, by, bz, 0, n, halo_full);
+                    tma::tensor_g2s_5d(rows + rt * HSLOT, &map_gout, bx, by, bz, 0, n, &halo_full[b]);
+                    if (gate) tma::tensor_g2s_5d(orows + rt * HSLOT, &map_out, bx, by, bz, 0, n, &halo_full[b]);
                 }
             };
             uint32_t it = 0, tcount = 0, s = 0, ph = 0;
-            if ((long long)blockIdx.x < p.num_tiles) issue_halo(blockIdx.x);
-            const int halo_at = (ngroups < S ? ngroups : S) - 1;
+            if ((long long)blockIdx.x < p.num_tiles) issue_halo(blockIdx.x, 0);
             for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++tcount) {
                 const int tx_i = (int)(tile % p.tiles_x);
                 const int ty_i = (int)((tile / p.tiles_x) % p.tiles_y);
@@ -236,10 +243,9 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
                     // channels past C are outside the tensor maps: zero-filled, no traffic
                     tma::tensor_g2s_5d(stage, &map_in, x0, y0, z, g * CB, n, &full[s]);
                     tma::tensor_g2s_5d(stage + CB * CHAN, &map_gin, x0, y0, z, g * CB, n, &full[s]);
-                    if (g == halo_at && tile + gridDim.x < p.num_tiles) {
-                        split_wait(halo_empty, tcount & 1u, abort_flag, p.status, 5);
-                        issue_halo(tile + gridDim.x);
-                    }
+                    // the next tile's halo rows go out with this tile's first stage: their buffer was freed
+                    // a whole tile ago, so the builders never wait for a request that has not been made
+                    if (g == 0 && tile + gridDim.x < p.num_tiles) issue_halo(tile + gridDim.x, tcount + 1);
                     if (++s == (uint32_t)S) s = 0, ph ^= 1u;
                 }
             }
@@ -254,7 +260,9 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
                 const long long nz = tile / tiles_per_plane;
                 const int z = p.z0 + (int)(nz % p.ZW), n = (int)(nz / p.ZW);
                 const int x0 = tx_i * TX, y0 = ty_i * TR;
-                split_wait(halo_full, tcount & 1u, abort_flag, p.status, 6);
+                const int hb = tcount & 1;
+                float *rows = rows0 + hb * HBUF, *orows = rows + RT * HSLOT;
+                split_wait(&halo_full[hb], (tcount >> 1) & 1u, abort_flag, p.status, 6);
                 split_fill_rows(p, rows, orows, HSLOT, TXP, gate, btid, n, z, y0, x0);
                 if (tcount) split_wait(m_done, (tcount - 1) & 1u, abort_flag, p.status, 7);  // the previous table has been read
                 tma::named_barrier(3, kSplitBuilders);
@@ -262,7 +270,7 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the reads of the rows, before TMA rewrites them
                 tma::named_barrier(3, kSplitBuilders);
                 if (btid == 0) {
-                    tma::mbar_arrive(halo_empty);  // the TMA slots may take the next tile's rows
+                    tma::mbar_arrive(&halo_empty[hb]);  // the TMA slots may take the rows of the tile after next
                     tma::mbar_arrive(table_full);
                 }
             }

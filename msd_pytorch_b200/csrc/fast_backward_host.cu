@@ -79,9 +79,9 @@ static bool plan(const BackwardArgs &a, BwdPlan *pl) {
     const int TX = pl->txq16 ? 64 : 128;
     if (nd == 3 && do_x && do_k && (g.x % 128) == 0 && a.d <= kSplitMaxDilation && C >= split_min_channels(a.d) && tuning_get(BWD3D, a.d) != 0) {
         // role-split kernel: 4 X warps + 8 K warps on tiles of 4 rows x 128 columns, kSplitCB
-        // channels per ring stage; the table of M (27 taps x (4 x 128 + 4) floats) beside the halo rows
+        // channels per ring stage; the table of M (27 taps x (4 x 128 + 4) floats) beside the (double-buffered) halo rows
         const int TR = kSplitRows, TXP = 128 + 2 * Dp;
-        const size_t halo = (size_t)RT * ((TR * TXP + 31) & ~31) * (a.out ? 2 : 1) + ((27 * (TR * 128 + 4) + 31) & ~31);
+        const size_t halo = 2 * (size_t)RT * ((TR * TXP + 31) & ~31) * (a.out ? 2 : 1) + ((27 * (TR * 128 + 4) + 31) & ~31);  // two halo buffers + the table
         const size_t fixed = kSplitHeader + (size_t)4 * (C * TAPS_PAD + (size_t)kSplitKWarps * C * 28 + halo);
         const size_t stage = (size_t)4 * 2 * kSplitCB * TR * 128;
         if (fixed + 2 * stage <= kSmemBudget) {
