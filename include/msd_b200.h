@@ -240,7 +240,7 @@ MSD_API int msd_slab_layer_backward(const msd_tensor_t *result, const msd_tensor
  * (family: 0 = 2D forward, 1 = 2D backward, 2 = 3D forward, 3 = 3D backward).
  * 3D backward: variant 0 = one kind of consumer warp computes both gradients,
  * variant 1 (default) = warps split by role (input-gradient warps, weight-gradient
- * warps, table builders) for layers with 8 (dilation <= 5) or 12 and more input
+ * warps, table builders) for layers with 8 (dilation <= 5) or 10 and more input
  * channels whose x extent is a multiple of 128; variant 2 = the input gradient as a
  * TF32 tensor-core contraction with error-compensated operand splitting (tcgen05,
  * float32-level accuracy), the weight gradient on the CUDA cores (8 to ~88 input

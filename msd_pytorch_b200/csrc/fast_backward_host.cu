@@ -51,7 +51,7 @@ struct BwdPlan {
 static const int kSplitRows = 4, kSplitKWarps = 8, kSplitCB = 4, kSplitMaxDilation = 12, kSplitMaxStages = 8, kSplitHeader = 512;
 // below this many input channels the per-tile set-up of the split kernel outweighs its faster
 // channel loop (large dilations have more border tiles, whose set-up reads global memory)
-static int split_min_channels(int d) { return d <= 5 ? 8 : 12; }
+static int split_min_channels(int d) { return d <= 5 ? 8 : 10; }
 // tensor-core kernel (fast_backward3d_hybrid.cuh): rows per tile, channels per ring stage, most ring stages, fewest channels
 static const int kMmaRowsHost = 2, kMmaCBHost = 8, kMmaMaxStagesHost = 8, kMmaMinChannels = 8;
 

@@ -186,7 +186,7 @@ def test_forward3d_launch_variants(cc, cuda_device, d, variant):
 
 @pytest.mark.parametrize("sp,B,depth", [((13, 23, 256), 2, 22), ((10, 11, 128), 1, 30), ((24, 40, 384), 1, 15)])
 def test_backward3d_role_split_variant(cuda_device, sp, B, depth):
-    """The role-split 3D backward (variant 1: X warps + K warps; layers of 8 (12 for dilations above 5) and more input
+    """The role-split 3D backward (variant 1: X warps + K warps; layers of 8 (10 for dilations above 5) and more input
     channels) == the three single ops per layer, which the tests above hold against the oracle:
     ragged tiles in y, one and several tiles in x (both x borders in one tile when X == 128),
     every dilation 1..10, channel counts that are and are not multiples of the stage's 4."""
@@ -267,7 +267,7 @@ def test_role_split_3d_backward_against_cpu_oracle(cuda_device, sp):
         res.backward(gout.to(dev))
         torch.cuda.synchronize()
         # layers with >= 8 input channels (dilation <= 5) or >= 12 (above) take the split kernel
-        expect = sum(1 for i in range(depth) if 1 + i >= (8 if dil[i] <= 5 else 12))
+        expect = sum(1 for i in range(depth) if 1 + i >= (8 if dil[i] <= 5 else 10))
         assert L.msd_split_launch_count() - split0 == expect
         assert _lib.device_status(dev) == 0
     finally:

@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 @pytest.mark.parametrize("X,depth", [(136, 7), (128, 15)])
 @pytest.mark.parametrize("world", [2, 3])
 def test_virtual_slabs_match_single_device(cuda_device, world, X, depth):
-    # X = 128 with 8 (12 for dilations above 5) and more input channels runs the role-split 3D backward in slab mode
+    # X = 128 with 8 (10 for dilations above 5) and more input channels runs the role-split 3D backward in slab mode
     from msd_pytorch_b200 import _lib
     from msd_pytorch_b200.distributed import SlabBlock, SlabPlan, VirtualRanks, slab_backward, slab_forward
     from msd_pytorch_b200.msd_block import block_backward_, block_forward_
