@@ -652,7 +652,7 @@ def ref_cuda_seconds(cfg, device, steps=2):
     return statistics.median(times)
 
 
-def run_one_layer(spec, device, reps=3):
+def run_one_layer(spec, device, reps=10):
     """`--one-layer cfg:channels:dilation`: a few launches of one layer's forward and fused
     backward on the configuration's shape, timed with CUDA events (the profiling target)."""
     from msd_pytorch_b200 import msd_custom_convolutions as cc

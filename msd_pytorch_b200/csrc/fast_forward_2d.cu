@@ -103,7 +103,7 @@ template <int D, int R, int Q, int K, int NT, int TW>
 static int launch_fwd2d(const CUtensorMap &map, const Fwd2dParams &p, int grid, int stages, cudaStream_t s) {
     using Cfg = Fwd2dCfg<D, R, Q, K, TW>;
     auto kern = forward2d_kernel<D, R, Q, K, NT, TW>;
-    const size_t smem = 256 + (size_t)stages * Cfg::STAGE_BYTES + (size_t)((p.C * (NT == 3 ? 28 : 12) + 31) & ~31) * 4;
+    const size_t smem = 256 + (size_t)stages * Cfg::STAGE_BYTES + (size_t)((p.C * fwd_weight_floats(NT) + 31) & ~31) * 4;
     MSD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     MSD_CUDA_TRY(tma::launch_pdl(kern, dim3(grid), dim3(Cfg::THREADS), smem, s, map, p));
     return MSD_OK;
@@ -120,18 +120,23 @@ static int launch_fwd2d(const CUtensorMap &map, const Fwd2dParams &p, int grid, 
 //   variant 2: 6-row lattice, 4 segments, 128 columns
 //   variant 3: 4-row lattice, 2 segments, 64 columns (twice the tiles: finer load balance)
 //   variant 4: 3-row lattice, taller stacks (Q chosen for 36..48 rows), 4 segments, 128 columns
-static const int kNumFwd2dVariants = 5;
+//   variant 5: 8-row lattice (fewest shared loads per FMA), 4 segments, 128 columns
+//   variant 6: 6-row lattice, 2 segments (twice the warps), 128 columns
+//   variant 7: tiles of 60..64 rows with ONE row stack where the dilation allows (lattices of 6..15
+//              rows: the taller the lattice, the fewer shared loads per FMA), 4 segments
+//   variant 8: the same with 2 segments (twice the warps)
+static const int kNumFwd2dVariants = 9;
 static const Fwd2dVariant kFwd2d[10][kNumFwd2dVariants] = {
-    {V(1, 4, 8, 4, 1, 128), V(1, 4, 8, 2, 1, 128), V(1, 6, 8, 4, 1, 128), V(1, 4, 8, 2, 1, 64), V(1, 3, 14, 4, 1, 128)},
-    {V(2, 4, 4, 4, 1, 128), V(2, 4, 4, 2, 1, 128), V(2, 6, 4, 4, 1, 128), V(2, 4, 4, 2, 1, 64), V(2, 3, 7, 4, 1, 128)},
-    {V(3, 4, 3, 4, 1, 128), V(3, 4, 3, 2, 1, 128), V(3, 6, 3, 4, 1, 128), V(3, 4, 3, 2, 1, 64), V(3, 3, 5, 4, 1, 128)},
-    {V(4, 4, 2, 4, 1, 128), V(4, 4, 2, 2, 1, 128), V(4, 6, 2, 4, 1, 128), V(4, 4, 2, 2, 1, 64), V(4, 3, 4, 4, 1, 128)},
-    {V(5, 4, 2, 4, 1, 128), V(5, 4, 2, 2, 1, 128), V(5, 6, 2, 4, 1, 128), V(5, 4, 2, 2, 1, 64), V(5, 3, 3, 4, 1, 128)},
-    {V(6, 4, 2, 4, 1, 128), V(6, 4, 2, 2, 1, 128), V(6, 6, 2, 4, 1, 128), V(6, 4, 2, 2, 1, 64), V(6, 3, 2, 4, 1, 128)},
-    {V(7, 4, 2, 4, 1, 128), V(7, 4, 2, 2, 1, 128), V(7, 6, 1, 4, 1, 128), V(7, 4, 2, 2, 1, 64), V(7, 3, 2, 4, 1, 128)},
-    {V(8, 4, 1, 4, 1, 128), V(8, 4, 1, 2, 1, 128), V(8, 6, 1, 4, 1, 128), V(8, 4, 1, 2, 1, 64), V(8, 3, 2, 4, 1, 128)},
-    {V(9, 4, 1, 4, 1, 128), V(9, 4, 1, 2, 1, 128), V(9, 6, 1, 4, 1, 128), V(9, 4, 1, 2, 1, 64), V(9, 3, 1, 4, 1, 128)},
-    {V(10, 4, 1, 4, 1, 128), V(10, 4, 1, 2, 1, 128), V(10, 6, 1, 4, 1, 128), V(10, 4, 1, 2, 1, 64), V(10, 3, 1, 4, 1, 128)},
+    {V(1, 4, 8, 4, 1, 128), V(1, 4, 8, 2, 1, 128), V(1, 6, 8, 4, 1, 128), V(1, 4, 8, 2, 1, 64), V(1, 3, 14, 4, 1, 128), V(1, 8, 8, 4, 1, 128), V(1, 6, 8, 2, 1, 128), V(1, 15, 4, 4, 1, 128), V(1, 15, 4, 2, 1, 128)},
+    {V(2, 4, 4, 4, 1, 128), V(2, 4, 4, 2, 1, 128), V(2, 6, 4, 4, 1, 128), V(2, 4, 4, 2, 1, 64), V(2, 3, 7, 4, 1, 128), V(2, 8, 4, 4, 1, 128), V(2, 6, 4, 2, 1, 128), V(2, 15, 2, 4, 1, 128), V(2, 15, 2, 2, 1, 128)},
+    {V(3, 4, 3, 4, 1, 128), V(3, 4, 3, 2, 1, 128), V(3, 6, 3, 4, 1, 128), V(3, 4, 3, 2, 1, 64), V(3, 3, 5, 4, 1, 128), V(3, 8, 2, 4, 1, 128), V(3, 6, 3, 2, 1, 128), V(3, 10, 2, 4, 1, 128), V(3, 10, 2, 2, 1, 128)},
+    {V(4, 4, 2, 4, 1, 128), V(4, 4, 2, 2, 1, 128), V(4, 6, 2, 4, 1, 128), V(4, 4, 2, 2, 1, 64), V(4, 3, 4, 4, 1, 128), V(4, 8, 2, 4, 1, 128), V(4, 6, 2, 2, 1, 128), V(4, 15, 1, 4, 1, 128), V(4, 15, 1, 2, 1, 128)},
+    {V(5, 4, 2, 4, 1, 128), V(5, 4, 2, 2, 1, 128), V(5, 6, 2, 4, 1, 128), V(5, 4, 2, 2, 1, 64), V(5, 3, 3, 4, 1, 128), V(5, 8, 1, 4, 1, 128), V(5, 6, 1, 2, 1, 128), V(5, 12, 1, 4, 1, 128), V(5, 12, 1, 2, 1, 128)},
+    {V(6, 4, 2, 4, 1, 128), V(6, 4, 2, 2, 1, 128), V(6, 6, 2, 4, 1, 128), V(6, 4, 2, 2, 1, 64), V(6, 3, 2, 4, 1, 128), V(6, 8, 1, 4, 1, 128), V(6, 6, 1, 2, 1, 128), V(6, 10, 1, 4, 1, 128), V(6, 10, 1, 2, 1, 128)},
+    {V(7, 4, 2, 4, 1, 128), V(7, 4, 2, 2, 1, 128), V(7, 6, 1, 4, 1, 128), V(7, 4, 2, 2, 1, 64), V(7, 3, 2, 4, 1, 128), V(7, 8, 1, 4, 1, 128), V(7, 6, 1, 2, 1, 128), V(7, 9, 1, 4, 1, 128), V(7, 9, 1, 2, 1, 128)},
+    {V(8, 4, 1, 4, 1, 128), V(8, 4, 1, 2, 1, 128), V(8, 6, 1, 4, 1, 128), V(8, 4, 1, 2, 1, 64), V(8, 3, 2, 4, 1, 128), V(8, 8, 1, 4, 1, 128), V(8, 6, 1, 2, 1, 128), V(8, 8, 1, 4, 1, 128), V(8, 8, 1, 2, 1, 128)},
+    {V(9, 4, 1, 4, 1, 128), V(9, 4, 1, 2, 1, 128), V(9, 6, 1, 4, 1, 128), V(9, 4, 1, 2, 1, 64), V(9, 3, 1, 4, 1, 128), V(9, 8, 1, 4, 1, 128), V(9, 6, 1, 2, 1, 128), V(9, 7, 1, 4, 1, 128), V(9, 7, 1, 2, 1, 128)},
+    {V(10, 4, 1, 4, 1, 128), V(10, 4, 1, 2, 1, 128), V(10, 6, 1, 4, 1, 128), V(10, 4, 1, 2, 1, 64), V(10, 3, 1, 4, 1, 128), V(10, 8, 1, 4, 1, 128), V(10, 6, 1, 2, 1, 128), V(10, 6, 1, 4, 1, 128), V(10, 6, 1, 2, 1, 128)},
 };
 // 3D (three z-taps per staged plane), per dilation: variant 0 = 4-row lattice, 4 column
 // segments per thread; variant 1 = 4-row lattice, 2 segments (twice the warps, shorter tiles
@@ -162,10 +167,13 @@ int num_variants(int family) {
 
 static bool fwd_plan(const View &in, int nd, int d, const Fwd2dVariant **var, int *stages) {
     if (d < 1 || d > 10) return false;
-    const int wp = nd == 3 ? 28 : 12;
+    const int wp = fwd_weight_floats(nd == 3 ? 3 : 1);
     const int nvar = nd == 3 ? kNumFwd3dVariants : kNumFwd2dVariants;
     int v = tuning_get(nd == 3 ? FWD3D : FWD2D, d);
-    if (v < 0 || v >= nvar) v = 0;
+    // untuned 2D: the variants that won on a large image (16 x 1024 x 1024, where the number of
+    // tiles per SM does not matter); the autotuner refines this per shape
+    static const int kFwd2dDefault[10] = {5, 5, 6, 5, 2, 2, 8, 8, 8, 6};
+    if (v < 0 || v >= nvar) v = nd == 3 ? 0 : kFwd2dDefault[d - 1];
     const Fwd2dVariant *cand = nd == 3 ? &kFwd3d[d - 1][v] : &kFwd2d[d - 1][v];
     const size_t fixed = 256 + (size_t)((in.c * wp + 31) & ~31) * 4;
     if (fixed + 2 * (size_t)cand->stage_bytes > kFwdSmemBudget) {

@@ -134,7 +134,7 @@ def test_fused_block_backward_matches_separate_ops(cuda_device, nd):
     assert torch.equal(g1[:, :1], g3[:, :1]) and torch.equal(gb1, gb3) and all(torch.equal(a, b) for a, b in zip(gw1, gw3))
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2, 3, 4])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3, 4, 5, 6, 7, 8])
 @pytest.mark.parametrize("d", [1, 2, 3, 4, 5, 6, 7, 8, 9, 10])
 def test_forward_launch_variants(cc, cuda_device, d, variant):
     """Every tile-shape variant of the TMA forward gives the oracle's result, including
@@ -143,7 +143,7 @@ def test_forward_launch_variants(cc, cuda_device, d, variant):
     from oracle import msd_oracle as O
 
     dev = cuda_device
-    assert _lib.lib.msd_tuning_num_variants(_lib.FAMILY_FWD2D) == 5
+    assert _lib.lib.msd_tuning_num_variants(_lib.FAMILY_FWD2D) == 9
     _lib.check(_lib.lib.msd_tuning_set(_lib.FAMILY_FWD2D, d, variant))
     try:
         x, k, b, go = util.make_op_inputs(3, 4, 1, (150, 300), torch.float32, 40 + d, dev)
