@@ -299,8 +299,10 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
         // Rows within d of a y (z) border also collect a mirrored source row; those few are
         // fetched with plain loads.
         const bool fold_rows = (y0 < p.d) || (y0 + TR + p.d > p.Y) || (ND == 3 && (z < p.d || z + p.d >= p.Z));
-        // (with an already gated gradient and no border rows the boxes are final as they landed)
-        for (int item = tid; (gate || fold_rows) && item < RT * TR * quads; item += kConsumers) {
+        // (with an already gated gradient and no border rows the boxes are final as they landed:
+        // no pass over them and no barrier - both conditions are uniform over the block)
+        const bool touch_rows = gate || fold_rows;
+        for (int item = tid; touch_rows && item < RT * TR * quads; item += kConsumers) {
             const int rowid = item / quads, q4 = item - rowid * quads;
             const int rt_ = rowid / TR;
             const int soff = rt_ * HSLOT + (rowid - rt_ * TR) * TXP + 4 * q4;  // slot of the row tap + row inside it
@@ -341,7 +343,7 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
             }
             *reinterpret_cast<float4 *>(rows + soff) = g;
         }
-        tma::named_barrier(1, kConsumers);
+        if (touch_rows) tma::named_barrier(1, kConsumers);
 
         // ---- per-thread M_t for its P voxels ----
         float M[TAPS][P];
@@ -395,11 +397,11 @@ fused_backward_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_c
                     float m2 = m2v[e];
                     if (fold_x) {  // block-uniform: only tiles next to the left / right border
                         const int q = x0 + i;
+                        // only the few lanes within d of the border load (a load by all lanes
+                        // with a stride of four floats costs four shared-memory wavefronts)
                         const bool f0 = q < p.X && q <= p.d - 1, f2 = q < p.X && q >= p.X - p.d;
-                        const float v0 = row[f0 ? p.d - 1 - q - x0 : i];
-                        const float v2 = row[f2 ? 2 * p.X - 1 - q - p.d - x0 : i];
-                        m0 += f0 ? v0 : 0.f;
-                        m2 += f2 ? v2 : 0.f;
+                        if (f0) m0 += row[p.d - 1 - q - x0];
+                        if (f2) m2 += row[2 * p.X - 1 - q - p.d - x0];
                     }
                     M[rt * 3 + 0][j * 4 + e] = m0;
                     M[rt * 3 + 1][j * 4 + e] = cv[e];
