@@ -159,7 +159,7 @@ def test_forward_launch_variants(cc, cuda_device, d, variant):
         _lib.lib.msd_tuning_set(_lib.FAMILY_FWD2D, d, -1)
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3])
 @pytest.mark.parametrize("d", [1, 2, 3, 4, 5, 6, 7, 8, 9, 10])
 def test_forward3d_launch_variants(cc, cuda_device, d, variant):
     """All variants of the 3D forward (plane-wise TMA kernel + z-gather) match the oracle on a
@@ -168,7 +168,7 @@ def test_forward3d_launch_variants(cc, cuda_device, d, variant):
     from oracle import msd_oracle as O
 
     dev = cuda_device
-    assert _lib.lib.msd_tuning_num_variants(_lib.FAMILY_FWD3D) == 3
+    assert _lib.lib.msd_tuning_num_variants(_lib.FAMILY_FWD3D) == 4
     _lib.check(_lib.lib.msd_tuning_set(_lib.FAMILY_FWD3D, d, variant))
     try:
         x, k, b, go = util.make_op_inputs(2, 3, 1, (11, 50, 140), torch.float32, 70 + d, dev)
