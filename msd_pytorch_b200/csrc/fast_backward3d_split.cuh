@@ -117,29 +117,64 @@ __device__ __forceinline__ void split_fill_rows(const BwdParams &p, float *rows,
     }
 }
 
+// Floats [S, S + 4) of the eight floats (a, b).
+template <int S>
+__device__ __forceinline__ float4 split_shift4(const float4 &a, const float4 &b) {
+    if (S == 0) return a;
+    if (S == 1) return make_float4(a.y, a.z, a.w, b.x);
+    if (S == 2) return make_float4(a.z, a.w, b.x, b.y);
+    return make_float4(a.w, b.x, b.y, b.z);
+}
+
 // Pass B: the table  msm[t * TS + row * 128 + i] = M_t at voxel (row, x0 + i),  t = (tz, ty, tx):
 // the row of m that tap (tz, ty) reads, shifted by -d (tx - 1) columns, plus the mirrored x
-// source next to the left (tx = 0) / right (tx = 2) border of the image.  One (tap, row) per
-// builder warp and step, lanes on consecutive floats: every load and store is conflict-free
-// whatever the shift.
-__device__ __forceinline__ void split_build_table(const BwdParams &p, const float *rows, float *msm, int HSLOT, int TXP, int TS, int btid, int x0) {
-    constexpr int TAPS = 27, TR = kSplitRows, TX = kSplitTX;
+// source next to the left (tx = 0) / right (tx = 2) border of the image.  One (row tap, row)
+// per builder warp and step, four consecutive floats per lane: five aligned 128-bit loads
+// (three when d is a multiple of 4) give the three x taps, combined by the shift d mod 4
+// (SH, uniform over the launch), and three 128-bit stores write them - no branch in the loop.
+// The builder warps share their schedulers with three consumer warps each, so what counts is
+// how few instructions a row takes (a version with one scalar load and store per float was
+// 2 - 4 % slower on layers of 25 and more channels).
+template <int SH>
+__device__ __forceinline__ void split_build_table_sh(const BwdParams &p, const float *rows, float *msm, int HSLOT, int TXP, int TS, int btid, int x0) {
+    constexpr int RT = 9, TR = kSplitRows, TX = kSplitTX;
     const bool fold_l = x0 == 0, fold_r = x0 + TX == p.X;
-    const int lane = btid & 31;
-#pragma unroll 4
-    for (int item = btid >> 5; item < TAPS * TR; item += kSplitBuilderWarps) {
-        const int t = item / TR, rr = item - t * TR;
-        const int rt = t / 3, tx = t - 3 * rt;
+    const int lane = btid & 31, qd = p.d >> 2;
+    const bool lane_l = fold_l && 4 * lane < p.d, lane_r = fold_r && 4 * lane + 3 >= TX - p.d;
+#pragma unroll 2
+    for (int item = btid >> 5; item < RT * TR; item += kSplitBuilderWarps) {
+        const int rt = item / TR, rr = item - rt * TR;
         const float *row = rows + rt * HSLOT + rr * TXP + p.Dp;  // row[i] <-> image x = x0 + i
-        const float *src = row - p.d * (tx - 1) + lane;
-        float v[TX / 32];
+        const float4 *row4 = reinterpret_cast<const float4 *>(row);
+        const float4 c = row4[lane];
+        const float4 u0 = row4[lane + qd];  // floats [4 lane + d, ...): tap tx = 0
+        const float4 q0 = SH == 0 ? u0 : split_shift4<SH>(u0, row4[lane + qd + 1]);
+        const float4 l1 = row4[lane - qd];  // floats [4 lane - d, ...): tap tx = 2
+        const float4 q2 = SH == 0 ? l1 : split_shift4<(4 - SH) & 3>(row4[lane - qd - 1], l1);
+        float v0[4] = {q0.x, q0.y, q0.z, q0.w}, v2[4] = {q2.x, q2.y, q2.z, q2.w};
+        if (lane_l) {  // columns i <= d - 1 also get the source d - 1 - i
 #pragma unroll
-        for (int k = 0; k < TX / 32; ++k) v[k] = src[32 * k];
-        if (tx == 0 && fold_l && lane < p.d) v[0] += row[p.d - 1 - lane];                  // columns q <= d - 1 also get the source d - 1 - q
-        if (tx == 2 && fold_r && lane >= 32 - p.d) v[TX / 32 - 1] += row[TX + 31 - p.d - lane];  // columns q >= X - d also get 2X - 1 - q - d
-        float *dst = msm + t * TS + rr * TX + lane;
+            for (int e = 0; e < 4; ++e)
+                if (4 * lane + e < p.d) v0[e] += row[p.d - 1 - 4 * lane - e];
+        }
+        if (lane_r) {  // columns i >= X - d also get 2X - 1 - i - d
 #pragma unroll
-        for (int k = 0; k < TX / 32; ++k) dst[32 * k] = v[k];
+            for (int e = 0; e < 4; ++e)
+                if (4 * lane + e >= TX - p.d) v2[e] += row[2 * TX - 1 - p.d - 4 * lane - e];
+        }
+        float *dst = msm + (3 * rt) * TS + rr * TX + 4 * lane;
+        *reinterpret_cast<float4 *>(dst) = make_float4(v0[0], v0[1], v0[2], v0[3]);
+        *reinterpret_cast<float4 *>(dst + TS) = c;
+        *reinterpret_cast<float4 *>(dst + 2 * TS) = make_float4(v2[0], v2[1], v2[2], v2[3]);
+    }
+}
+
+__device__ __forceinline__ void split_build_table(const BwdParams &p, const float *rows, float *msm, int HSLOT, int TXP, int TS, int btid, int x0) {
+    switch (p.d & 3) {
+        case 0: split_build_table_sh<0>(p, rows, msm, HSLOT, TXP, TS, btid, x0); break;
+        case 1: split_build_table_sh<1>(p, rows, msm, HSLOT, TXP, TS, btid, x0); break;
+        case 2: split_build_table_sh<2>(p, rows, msm, HSLOT, TXP, TS, btid, x0); break;
+        default: split_build_table_sh<3>(p, rows, msm, HSLOT, TXP, TS, btid, x0); break;
     }
 }
 
