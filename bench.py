@@ -29,6 +29,10 @@ depends on the sample size.
 `--one-layer c4:50:2` runs a few launches of ONE layer's forward and fused backward on the
 named configuration's shape (here: 50 input channels, dilation 2) and prints their times;
 it is the command the ncu summaries under profiles/ are captured from.
+
+`--layer-table c2` times single layers of the configuration's shape over a grid of channel
+counts and dilations, each as a CUDA graph of ten launches (device time only, no host gaps),
+and prints one JSON line per dilation: what a layer costs per input channel and per launch.
 """
 import argparse
 import json
@@ -687,6 +691,58 @@ def run_one_layer(spec, device, reps=10):
     print(json.dumps(out), flush=True)
 
 
+def run_layer_table(name, device, reps=10):
+    """`--layer-table cfg`: microseconds of one layer's forward and of its fused backward (with
+    the small reduction kernels of a one-layer block backward) against the number of input
+    channels, for four dilations; each figure is a CUDA graph of `reps` launches replayed twice."""
+    from msd_pytorch_b200 import msd_custom_convolutions as cc
+    from msd_pytorch_b200.msd_block import block_backward_
+
+    cfg = CONFIGS[name]
+    nd, batch, sp = cfg["ndim"], cfg["batch"], cfg["spatial"]
+    if name == "c5":
+        sp = (64,) + tuple(sp[1:])
+    channels = [c for c in (1, 4, 10, 25, 50, 100) if c <= cfg["depth"]]
+    g = torch.Generator(device=device).manual_seed(0)
+    top = max(channels)
+    res = torch.rand(batch, top + 1, *sp, device=device, generator=g)
+    grad = torch.randn(batch, top + 1, *sp, device=device, generator=g)
+    b = torch.zeros(1, device=device)
+    vox = voxels_of(batch, sp)
+    peak, _ = measured_peak()
+
+    def graph_us(fn):
+        fn()
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            for _ in range(reps):
+                fn()
+        gr.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        gr.replay()
+        gr.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (2 * reps) * 1e3
+
+    for d in (1, 3, 6, 10):
+        row = {"config": name, "dilation": d, "channels": channels, "forward_us": [], "forward_frac": [], "backward_us": [], "backward_frac": []}
+        for c in channels:
+            w = torch.randn(1, c, *([3] * nd), device=device, generator=g) * 0.1
+            gw, gb = torch.zeros_like(w), torch.zeros(1, device=device)
+            r, gr_ = res[:, :c + 1], grad[:, :c + 1]
+            us = graph_us(lambda: cc.conv_relu_forward(res[:, :c], w, b, res[:, top:top + 1], d))
+            row["forward_us"].append(round(us, 1))
+            row["forward_frac"].append(round(4 * vox * (c + 1) / us / 1e3 / peak, 3))
+            us = graph_us(lambda: block_backward_(r, gr_, c, [d], [w], [gw], gb))
+            row["backward_us"].append(round(us, 1))
+            row["backward_frac"].append(round(4 * vox * (3 * c + 2) / us / 1e3 / peak, 3))
+        print(json.dumps(row), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -700,6 +756,7 @@ def main():
     ap.add_argument("--no-autotune", action="store_true", help="use the library's default launch variants")
     ap.add_argument("--no-extra-configs", action="store_true", help="skip the c4 / c5_zslab records that follow the default config's line")
     ap.add_argument("--one-layer", default=None, metavar="CFG:CHANNELS:DILATION", help="time one layer's kernels (profiling target) and exit")
+    ap.add_argument("--layer-table", default=None, metavar="CFG", choices=sorted(CONFIGS), help="time single layers over channel counts and dilations (CUDA graphs) and exit")
     ap.add_argument("--force-variant", default=None, metavar="FAMILY=V[,FAMILY=V]",
                     help="force a launch variant for all dilations (families: fwd2d, bwd2d, fwd3d, bwd3d); implies --no-autotune")
     args = ap.parse_args()
@@ -731,6 +788,15 @@ def main():
                 _lib.check(_lib.lib.msd_tuning_set(fam[name], d, int(v)))
     if args.one_layer:
         run_one_layer(args.one_layer, device)
+        return
+    if args.layer_table:
+        if not args.no_autotune:
+            from msd_pytorch_b200 import autotune
+
+            c = CONFIGS[args.layer_table]
+            sp = c["spatial"] if args.layer_table != "c5" else (32,) + tuple(c["spatial"][1:])
+            autotune.tune(c["batch"], sp, max(2, c["depth"] // 2), range(1, 11), device=device, reps=3)
+        run_layer_table(args.layer_table, device)
         return
     if world > 1:
         import torch.distributed as dist

@@ -182,7 +182,7 @@ static bool fwd_plan(const View &in, int nd, int d, const Fwd2dVariant **var, in
     // untuned 2D: the variants that won on a large image (16 x 1024 x 1024, where the number of
     // tiles per SM does not matter); the autotuner refines this per shape
     static const int kFwd2dDefault[10] = {5, 5, 6, 5, 2, 2, 8, 8, 8, 6};
-    if (v < 0 || v >= nvar) v = nd == 3 ? 0 : kFwd2dDefault[d - 1];
+    if (v < 0 || v >= nvar) v = nd == 3 ? 0 : (in.x <= 64 ? 3 : kFwd2dDefault[d - 1]);  // narrow images: the 64-column tiles
     const Fwd2dVariant *cand = nd == 3 ? &kFwd3d[d - 1][v] : &kFwd2d[d - 1][v];
     const size_t fixed = 256 + (size_t)((in.c * wp + 31) & ~31) * 4;
     if (fixed + 2 * (size_t)cand->stage_bytes > kFwdSmemBudget) {
