@@ -68,11 +68,11 @@ def algorithmic_bytes(depth, voxels):
 
 # DRAM traffic per launch measured by ncu (dram__bytes_read.sum + dram__bytes_write.sum) divided
 # by the algorithmic bytes of the captured launch (`--one-layer` captures summarised in profiles/):
-# 2D backward 1224.3 / 1275.1 MB and 2D forward 436.0 / 427.8 MB (c2:50:10); 3D backward
-# 2494.3 / 2550.1 MB (c4:50:2) and 3D forward 512.0 / 436.2 MB (c4:25:4, both forward kernels).
+# 2D backward 1226.2 / 1275.1 MB and 2D forward 430.1 / 427.8 MB (c2:50:10); 3D backward
+# 2495.0 / 2550.1 MB (c4:50:2) and 3D forward 509.8 / 436.2 MB (c4:25:4, both forward kernels).
 # Traffic grows with the channel count like the algorithmic bytes do, so the ratio is applied to
 # the average launch.
-NCU_TRAFFIC_RATIO = {("bwd", 2): 1224.3 / 1275.1, ("fwd", 2): 436.0 / 427.8, ("bwd", 3): 2494.3 / 2550.1, ("fwd", 3): 512.0 / 436.2}
+NCU_TRAFFIC_RATIO = {("bwd", 2): 1226.2 / 1275.1, ("fwd", 2): 430.1 / 427.8, ("bwd", 3): 2495.0 / 2550.1, ("fwd", 3): 509.8 / 436.2}
 
 
 def measured_peak():
@@ -359,7 +359,7 @@ def run_ours(args, name, cfg, rank, world, device, steps, warmup, full=True):
         "device_status": status,
         "clocks": clocks,
         "roofline": {
-            "kernel": ("fused_backward_kernel" if nd == 2 else "fused_backward3d_split_kernel (fused_backward_kernel<3> below 8 input channels)")
+            "kernel": ("fused_backward_kernel" if nd == 2 else "fused_backward_split_kernel<3> (fused_backward_kernel<3> below 8 input channels)")
             + " (one launch per layer; the small second-pass reductions are inside the timed span)",
             "bound": "hbm", "achieved": gbs_bwd, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": gbs_bwd / peak,
             "frac_of_nominal_8TBs": gbs_bwd / 8000.0,
@@ -545,7 +545,7 @@ def run_slab(args, cfg, rank, world, device, steps, warmup, full=True):
         "e2e": {"value": vox_total / (ms_e2e * 1e-3), "unit": "voxels/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": int(2 * vox_rank * 4), "d2h_bytes_per_step": 4},
         "gpu_launches": launches[0], "device_status": status, "clocks": clocks,
-        "roofline": {"kernel": "fused_backward3d_split_kernel (per rank; gradient hand-overs inside the timed span)", "bound": "hbm",
+        "roofline": {"kernel": "fused_backward_split_kernel<3> (per rank; gradient hand-overs inside the timed span)", "bound": "hbm",
                      "achieved": gbs_bwd, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": gbs_bwd / peak,
                      "algorithmic_bytes_per_launch": a_bwd / depth, "avg_launch_ms": ms_bwd / depth, "launches": depth,
                      "traffic": NCU_TRAFFIC_RATIO[("bwd", 3)] * a_bwd / depth,

@@ -12,7 +12,7 @@
 // gradient contracts over the voxels, 8 per instruction, into a skinny C x 27 result: on the
 // tensor cores it would need 40 clocks per voxel, more than the CUDA cores take for any C
 // below ~70 (a kernel that does so was built and measured: 3.5 x slower than this one's
-// predecessor).  So the weight gradient keeps the "K warps" of fast_backward3d_split.cuh,
+// predecessor).  So the weight gradient keeps the "K warps" of fast_backward_split.cuh,
 // and the warps that used to compute the input gradient with 27 x 4 FMAs per lane and channel
 // are gone.
 //
@@ -38,7 +38,7 @@
 // Requirements (checked by the host): X a multiple of 128, dilation <= 12, both gradients
 // wanted, the gradient channel already gated, at most 128 input channels.
 #pragma once
-#include "fast_backward3d_split.cuh"
+#include "fast_backward_split.cuh"
 #include "umma.cuh"
 
 namespace msd {

@@ -19,7 +19,7 @@ BwdLaunchFn bwd3d_launchers[2][3] = {
 };
 
 static int launch3d_split(const CUtensorMap *m, const BwdParams &p, int grid, size_t smem, cudaStream_t s) {
-    auto kern = fused_backward3d_split_kernel;
+    auto kern = fused_backward_split_kernel<3>;
     MSD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     MSD_CUDA_TRY(tma::launch_pdl(kern, dim3(grid), dim3(kSplitThreads), smem, s, m[0], m[1], m[2], m[3], p));
     return MSD_OK;

@@ -15,6 +15,7 @@ size_t bwd3d_hybrid_smem(int C, int Dp, int stages);
 extern BwdLaunchFn bwd2d_launchers[2][2][3];
 extern BwdLaunchFn bwd3d_launchers[2][3];
 extern BwdLaunchFn bwd3d_split_launcher;
+extern BwdLaunchFn bwd2d_split_launcher;
 
 
 static const int kMaxFastDilation = 16;
@@ -43,7 +44,7 @@ static bool aligned_view(const View *v) {
 struct BwdPlan {
     int txq16, j, stages, blocks_per_sm;
     size_t smem;
-    bool split;  // 3D kernel with X warps and K warps (fast_backward3d_split.cuh)
+    bool split;  // kernel with X warps and K warps (fast_backward_split.cuh)
     bool mma;    // 3D kernel with the input gradient on the tensor cores (fast_backward3d_hybrid.cuh)
 };
 
@@ -77,12 +78,14 @@ static bool plan(const BackwardArgs &a, BwdPlan *pl) {
         }
     }
     const int TX = pl->txq16 ? 64 : 128;
-    if (nd == 3 && do_x && do_k && (g.x % 128) == 0 && a.d <= kSplitMaxDilation && C >= split_min_channels(a.d) && tuning_get(BWD3D, a.d) != 0) {
+    const bool split3d = nd == 3 && C >= split_min_channels(a.d) && tuning_get(BWD3D, a.d) != 0;
+    const bool split2d = nd == 2 && tuning_get(BWD2D, a.d) == 2;
+    if ((split3d || split2d) && do_x && do_k && (g.x % 128) == 0 && a.d <= kSplitMaxDilation) {
         // role-split kernel: 4 X warps + 8 K warps on tiles of 4 rows x 128 columns, kSplitCB
-        // channels per ring stage; the table of M (27 taps x (4 x 128 + 4) floats) beside the (double-buffered) halo rows
+        // channels per ring stage; the table of M (27 or 9 taps x (4 x 128 + 4) floats) beside the (double-buffered) halo rows
         const int TR = kSplitRows, TXP = 128 + 2 * Dp;
-        const size_t halo = 2 * (size_t)RT * ((TR * TXP + 31) & ~31) * (a.out ? 2 : 1) + ((27 * (TR * 128 + 4) + 31) & ~31);  // two halo buffers + the table
-        const size_t fixed = kSplitHeader + (size_t)4 * (C * TAPS_PAD + (size_t)kSplitKWarps * C * 28 + halo);
+        const size_t halo = 2 * (size_t)RT * ((TR * TXP + 31) & ~31) * (a.out ? 2 : 1) + ((3 * RT * (TR * 128 + 4) + 31) & ~31);  // two halo buffers + the table
+        const size_t fixed = kSplitHeader + (size_t)4 * (C * TAPS_PAD + (size_t)kSplitKWarps * C * TAPS_PAD + halo);
         const size_t stage = (size_t)4 * 2 * kSplitCB * TR * 128;
         if (fixed + 2 * stage <= kSmemBudget) {
             int s = (int)((kSmemBudget - fixed) / stage);
@@ -303,7 +306,8 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
                 if (rc2) return rc2;
                 continue;
             }
-            int box[5] = {which < 2 ? TX : TX + 2 * p.Dp, TR, 1, (which < 2) ? (pl.split ? kSplitCB : pl.mma ? kMmaCBHost : 1) : 1, 1};
+            const int cbox = (which < 2) ? (pl.split ? kSplitCB : pl.mma ? kMmaCBHost : 1) : 1;  // channels per box
+            int box[5] = {which < 2 ? TX : TX + 2 * p.Dp, TR, a.nd == 3 ? 1 : cbox, a.nd == 3 ? cbox : 1, 1};
             int64_t dims[5], strides[5];
             if (a.nd == 3) {
                 dims[0] = v->x, dims[1] = v->y, dims[2] = v->z, dims[3] = v->c, dims[4] = v->n;
@@ -317,7 +321,8 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
         }
     }
     const int mode = do_x && do_k ? 2 : (do_k ? 1 : 0);
-    BwdLaunchFn fn = a.nd == 3 ? (pl.mma ? bwd3d_hybrid_launcher : pl.split ? bwd3d_split_launcher : bwd3d_launchers[pl.txq16][mode]) : bwd2d_launchers[pl.txq16][pl.j - 1][mode];
+    BwdLaunchFn fn = a.nd == 3 ? (pl.mma ? bwd3d_hybrid_launcher : pl.split ? bwd3d_split_launcher : bwd3d_launchers[pl.txq16][mode])
+                               : (pl.split ? bwd2d_split_launcher : bwd2d_launchers[pl.txq16][pl.j - 1][mode]);
     int rc = fn(maps, p, grid, pl.smem, s);
     if (rc) return rc;
     count_launch(true);

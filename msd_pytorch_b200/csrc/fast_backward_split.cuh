@@ -1,37 +1,41 @@
-// Fused backward of one 3D MSD layer (one output channel, float32) with the consumer warps
-// split by role.  Same mathematics and buffers as fused_backward_kernel (fast_backward.cuh);
-// what differs is who computes what:
+// Fused backward of one MSD layer (one output channel, float32; 3D and 2D) with the consumer
+// warps split by role.  Same mathematics and buffers as fused_backward_kernel
+// (fast_backward.cuh); what differs is who computes what:
 //
-//   X warps  voxels across lanes (4 consecutive x per thread), the 27 values M_t of each
-//            voxel in registers: per channel 27 x 4 FMAs update the input gradient, one
+//   X warps  voxels across lanes (4 consecutive x per thread), the 27 (9) values M_t of each
+//            voxel in registers: per channel 27 (9) x 4 FMAs update the input gradient, one
 //            128-bit store.  No reduction of any kind.
-//   K warps  lane = (quarter-warp, tap lane): each lane keeps M_t[v] for 4 taps (tap lane + 8 a)
+//   K warps  3D: lane = (quarter-warp, tap lane): each lane keeps M_t[v] for 4 taps (tap lane + 8 a)
 //            and 16 voxels of half a tile row in registers, reads in[c][v] with 128-bit
 //            shared loads and accumulates  sum_v in[c][v] * M_t[v]  with packed FMAs; the
 //            four quarter-warps' sums meet in a 3-shuffle reduce-scatter (the full shuffle
 //            tree of the unsplit kernel costs 124 instructions per 216 FMAs in 3D).
+//            2D: the same lanes; a lane keeps tap `tap lane` (0..7) for its 16 voxels and the
+//            ninth tap for two of them (the eight tap lanes of a quarter-warp share it out);
+//            five shuffles per channel.
 //
-// A tile is 4 rows x 128 columns of one z-plane.  The block has four warpgroups:
+// A tile is 4 rows x 128 columns of one z-plane (image).  The block has four warpgroups:
 //   warps 0-3    X warps, one per tile row               (registers raised to kSplitRegsX)
 //   warps 4-11   K warps, (row, half) = (w-4)/2, (w-4)%2 (the launch's 128 registers)
 //   warp 12      TMA producer                            (registers lowered to kSplitRegsP)
 //   warps 13-15  builders of the table of M (below)      (same warpgroup as the producer)
 // so that each of the four warp schedulers (warp id mod 4) carries one X warp and two K warps.
-// The register file is re-divided between the warpgroups with setmaxnreg: the X warps need
+// The register file is re-divided between the warpgroups with setmaxnreg: the 3D X warps need
 // 108 registers for M alone, the producer and the builders few.
 //
 // Data movement.  One ring stage holds kSplitCB consecutive channels of the tile: two TMA
 // boxes (activations, gradients) of kSplitCB x 4 x 128 floats, so that the cost of issuing a
-// copy and of the full/empty hand-shake is paid once per kSplitCB channels.  The 9 halo row
+// copy and of the full/empty hand-shake is paid once per kSplitCB channels.  The 9 (3) halo row
 // groups of gout (and of out, for the ReLU gate) land by TMA in one of two buffers (tiles
 // alternate), requested a whole tile ahead.  The builder warps turn them into
 // the table  Msm[t][row][x] = M_t(voxel)  in two short passes (gate + y/z folds in place; x
 // shifts + x folds into the table) while the consumers are still streaming the channels of
 // the previous tile; both kinds of consumer warps then fill their registers from the table
-// with aligned 128-bit loads and no arithmetic.  The table's tap stride is 4 mod 32 banks,
-// which makes the K warps' lane-per-tap loads conflict-free.  Hand-shakes: halo_full
-// (producer -> builders), halo_empty (builders -> producer), table_full (builders ->
-// consumers), m_done (consumers -> builders: the table may be overwritten).
+// with aligned 128-bit loads and no arithmetic - the per-tile set-up never holds the channel
+// stream up.  The table's tap stride is 4 mod 32 banks, which makes the K warps' lane-per-tap
+// loads conflict-free.  Hand-shakes: halo_full (producer -> builders), halo_empty (builders ->
+// producer), table_full (builders -> consumers), m_done (consumers -> builders: the table may
+// be overwritten).
 //
 // Requirements (checked by the host): X a multiple of 128, dilation <= 12, both gradients wanted.
 #pragma once
@@ -50,8 +54,7 @@ constexpr int kSplitKWarps = 2 * kSplitRows;
 constexpr int kSplitConsumerWarps = kSplitXWarps + kSplitKWarps;  // 12
 constexpr int kSplitConsumers = kSplitConsumerWarps * 32;         // 384
 constexpr int kSplitThreads = 512;                                // four warpgroups
-constexpr int kSplitWaccPad = 28;                                 // floats per (K warp, channel) slot
-constexpr int kSplitWPad = 28;                                    // floats per channel of weights in shared memory
+constexpr int split_taps_pad(int nd) { return nd == 3 ? 28 : 12; }  // floats per channel of weights / per (K warp, channel) slot in shared memory
 constexpr int kSplitMaxD = 12;                                    // border columns handled per side
 constexpr int kSplitMaxStages = 8;
 constexpr int kSplitHeaderBytes = 512;                            // barriers, abort flag, bias slots
@@ -69,11 +72,11 @@ __device__ __forceinline__ void split_wait(uint64_t *bar, uint32_t parity, volat
 // floats) into the rows of m, in place: ReLU gate, plus the mirrored y / z sources next to
 // the volume's borders.  Cooperative over the kSplitBuilders builder threads (index btid); the
 // caller synchronises them afterwards.
-template <int NTHREADS = kSplitBuilders, int TR = kSplitRows>
+template <int NTHREADS = kSplitBuilders, int TR = kSplitRows, int ND = 3>
 __device__ __forceinline__ void split_fill_rows(const BwdParams &p, float *rows, const float *orows, int HSLOT, int TXP, bool gate, int btid, int n,
                                                 int z, int y0, int x0) {
-    constexpr int RT = 9;
-    const bool fold_rows = (y0 < p.d) || (y0 + TR + p.d > p.Y) || (z < p.d || z + p.d >= p.Z);
+    constexpr int RT = ND == 3 ? 9 : 3;
+    const bool fold_rows = (y0 < p.d) || (y0 + TR + p.d > p.Y) || (ND == 3 && (z < p.d || z + p.d >= p.Z));
     if (!gate && !fold_rows) return;
     const float *go_n = p.gout + n * p.go_sn;
     const float *out_n = gate ? p.out + n * p.out_sn : nullptr;
@@ -93,11 +96,12 @@ __device__ __forceinline__ void split_fill_rows(const BwdParams &p, float *rows,
         }
         if (fold_rows) {
             const int y = y0 + rr, px = x0 - p.Dp + 4 * q4;
-            int zs[2], ys[2], nys = 0;
-            const int nzs = adjoint_sources_dev(z, rt / 3, p.d, p.Z, zs);
+            int zs[2], ys[2], nys = 0, nzs = 1;
+            zs[0] = 0;
+            if (ND == 3) nzs = adjoint_sources_dev(z, rt / 3, p.d, p.Z, zs);
             if (y < p.Y && nzs > 0) nys = adjoint_sources_dev(y, rt % 3, p.d, p.Y, ys);
             if (px >= 0 && px < p.X && nzs * nys > 0) {
-                const int dy = y - p.d * (rt % 3 - 1), dz = z - p.d * (rt / 3 - 1);
+                const int dy = y - p.d * (rt % 3 - 1), dz = ND == 3 ? z - p.d * (rt / 3 - 1) : 0;
                 for (int a = 0; a < nzs; ++a)
                     for (int b = 0; b < nys; ++b) {
                         if (ys[b] == dy && zs[a] == dz) continue;  // the TMA box already holds it
@@ -135,9 +139,9 @@ __device__ __forceinline__ float4 split_shift4(const float4 &a, const float4 &b)
 // The builder warps share their schedulers with three consumer warps each, so what counts is
 // how few instructions a row takes (a version with one scalar load and store per float was
 // 2 - 4 % slower on layers of 25 and more channels).
-template <int SH>
+template <int SH, int RT>
 __device__ __forceinline__ void split_build_table_sh(const BwdParams &p, const float *rows, float *msm, int HSLOT, int TXP, int TS, int btid, int x0) {
-    constexpr int RT = 9, TR = kSplitRows, TX = kSplitTX;
+    constexpr int TR = kSplitRows, TX = kSplitTX;
     const bool fold_l = x0 == 0, fold_r = x0 + TX == p.X;
     const int lane = btid & 31, qd = p.d >> 2;
     const bool lane_l = fold_l && 4 * lane < p.d, lane_r = fold_r && 4 * lane + 3 >= TX - p.d;
@@ -169,19 +173,31 @@ __device__ __forceinline__ void split_build_table_sh(const BwdParams &p, const f
     }
 }
 
+template <int RT>
 __device__ __forceinline__ void split_build_table(const BwdParams &p, const float *rows, float *msm, int HSLOT, int TXP, int TS, int btid, int x0) {
     switch (p.d & 3) {
-        case 0: split_build_table_sh<0>(p, rows, msm, HSLOT, TXP, TS, btid, x0); break;
-        case 1: split_build_table_sh<1>(p, rows, msm, HSLOT, TXP, TS, btid, x0); break;
-        case 2: split_build_table_sh<2>(p, rows, msm, HSLOT, TXP, TS, btid, x0); break;
-        default: split_build_table_sh<3>(p, rows, msm, HSLOT, TXP, TS, btid, x0); break;
+        case 0: split_build_table_sh<0, RT>(p, rows, msm, HSLOT, TXP, TS, btid, x0); break;
+        case 1: split_build_table_sh<1, RT>(p, rows, msm, HSLOT, TXP, TS, btid, x0); break;
+        case 2: split_build_table_sh<2, RT>(p, rows, msm, HSLOT, TXP, TS, btid, x0); break;
+        default: split_build_table_sh<3, RT>(p, rows, msm, HSLOT, TXP, TS, btid, x0); break;
     }
 }
 
+// One tiled TMA load of a (channels, rows, columns) box: 5-d maps (x, y, z, c, n) in 3D, 4-d maps
+// (x, y, c, n) in 2D.
+template <int ND>
+__device__ __forceinline__ void split_g2s(void *dst, const CUtensorMap *map, int x, int y, int z, int c, int n, uint64_t *bar) {
+    if (ND == 3)
+        tma::tensor_g2s_5d(dst, map, x, y, z, c, n, bar);
+    else
+        tma::tensor_g2s_4d(dst, map, x, y, c, n, bar);
+}
+
+template <int ND>
 __global__ void __launch_bounds__(kSplitThreads, 1)
-fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_gin,
-                              const __grid_constant__ CUtensorMap map_gout, const __grid_constant__ CUtensorMap map_out, const BwdParams p) {
-    constexpr int RT = 9, TAPS = 27;
+fused_backward_split_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_gin,
+                            const __grid_constant__ CUtensorMap map_gout, const __grid_constant__ CUtensorMap map_out, const BwdParams p) {
+    constexpr int RT = ND == 3 ? 9 : 3, TAPS = 3 * RT, WPAD = split_taps_pad(ND);
     constexpr int TX = kSplitTX, TR = kSplitRows, KH = kSplitKHalf, CB = kSplitCB;
     constexpr int CHAN = TR * TX;        // floats of one channel of one tensor in a stage
     constexpr int STAGE = 2 * CB * CHAN;  // CB channels of in, then CB channels of gin
@@ -204,7 +220,7 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
     float *msm = rows0 + 2 * HBUF;
     float *ring = msm + ((TAPS * TS + 31) & ~31);
     float *wsm = ring + (size_t)p.stages * STAGE;
-    float *wacc = wsm + p.C * kSplitWPad;
+    float *wacc = wsm + p.C * WPAD;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int S = p.stages;
@@ -224,11 +240,11 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
         *abort_flag = 0;
         tma::fence_barrier_init();
     }
-    for (int i = tid; i < p.C * kSplitWPad; i += kSplitThreads) {
-        const int c = i / kSplitWPad, t = i % kSplitWPad;
+    for (int i = tid; i < p.C * WPAD; i += kSplitThreads) {
+        const int c = i / WPAD, t = i % WPAD;
         wsm[i] = t < TAPS ? p.k[c * TAPS + t] : 0.f;
     }
-    for (int i = tid; i < kSplitKWarps * p.C * kSplitWaccPad; i += kSplitThreads) wacc[i] = 0.f;
+    for (int i = tid; i < kSplitKWarps * p.C * WPAD; i += kSplitThreads) wacc[i] = 0.f;
     tma::allow_dependents();
     __syncthreads();
     tma::grid_dependency_wait();
@@ -258,9 +274,9 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
                 tma::mbar_arrive_expect_tx(&halo_full[b], halo_bytes);
 #pragma unroll 1
                 for (int rt = 0; rt < RT; ++rt) {
-                    const int by = y0 + p.d * (1 - rt % 3), bz = z + p.d * (1 - rt / 3);
-                    tma::tensor_g2s_5d(rows + rt * HSLOT, &map_gout, bx, by, bz, 0, n, &halo_full[b]);
-                    if (gate) tma::tensor_g2s_5d(orows + rt * HSLOT, &map_out, bx, by, bz, 0, n, &halo_full[b]);
+                    const int by = y0 + p.d * (1 - rt % 3), bz = ND == 3 ? z + p.d * (1 - rt / 3) : 0;
+                    split_g2s<ND>(rows + rt * HSLOT, &map_gout, bx, by, bz, 0, n, &halo_full[b]);
+                    if (gate) split_g2s<ND>(orows + rt * HSLOT, &map_out, bx, by, bz, 0, n, &halo_full[b]);
                 }
             };
             uint32_t it = 0, tcount = 0, s = 0, ph = 0;
@@ -276,8 +292,8 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
                     tma::mbar_arrive_expect_tx(&full[s], (uint32_t)(STAGE * 4));
                     float *stage = ring + s * STAGE;
                     // channels past C are outside the tensor maps: zero-filled, no traffic
-                    tma::tensor_g2s_5d(stage, &map_in, x0, y0, z, g * CB, n, &full[s]);
-                    tma::tensor_g2s_5d(stage + CB * CHAN, &map_gin, x0, y0, z, g * CB, n, &full[s]);
+                    split_g2s<ND>(stage, &map_in, x0, y0, z, g * CB, n, &full[s]);
+                    split_g2s<ND>(stage + CB * CHAN, &map_gin, x0, y0, z, g * CB, n, &full[s]);
                     // the next tile's halo rows go out with this tile's first stage: their buffer was freed
                     // a whole tile ago, so the builders never wait for a request that has not been made
                     if (g == 0 && tile + gridDim.x < p.num_tiles) issue_halo(tile + gridDim.x, tcount + 1);
@@ -298,10 +314,10 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
                 const int hb = tcount & 1;
                 float *rows = rows0 + hb * HBUF, *orows = rows + RT * HSLOT;
                 split_wait(&halo_full[hb], (tcount >> 1) & 1u, abort_flag, p.status, 6);
-                split_fill_rows(p, rows, orows, HSLOT, TXP, gate, btid, n, z, y0, x0);
+                split_fill_rows<kSplitBuilders, kSplitRows, ND>(p, rows, orows, HSLOT, TXP, gate, btid, n, z, y0, x0);
                 if (tcount) split_wait(m_done, (tcount - 1) & 1u, abort_flag, p.status, 7);  // the previous table has been read
                 tma::named_barrier(3, kSplitBuilders);
-                split_build_table(p, rows, msm, HSLOT, TXP, TS, btid, x0);
+                split_build_table<RT>(p, rows, msm, HSLOT, TXP, TS, btid, x0);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the reads of the rows, before TMA rewrites them
                 tma::named_barrier(3, kSplitBuilders);
                 if (btid == 0) {
@@ -316,17 +332,17 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
     uint32_t tcount = 0, s = 0, ph = 0;
     if (warp >= kSplitXWarps) {
         // ===================================== K warps =====================================
-        // lane = tap (tz, ty, tx); Mk[v] = M_tap at voxel (row r, column x0 + KH * h + v)
+        const int kw = warp - kSplitXWarps, r = kw >> 1, h = kw & 1;
+        const int qw = lane >> 3, tl = lane & 7;
+        const bool hi = (lane & 16) != 0, mid = (lane & 8) != 0;
+        if constexpr (ND == 3) {
         // lane = (qw, tl): taps tl + 8 {0..3}; voxels 4 (4 j + qw) + {0..3}, j = 0..3, of the half row.
         // The four quarter-warps read four neighbouring 16-byte pieces of the activations per
         // load; the eight lanes of a quarter-warp (one phase of a 128-bit shared load) read
         // eight neighbouring taps of the table, whose tap stride of 4 mod 32 banks spreads them
         // over all banks.
-        const int kw = warp - kSplitXWarps, r = kw >> 1, h = kw & 1;
-        const int qw = lane >> 3, tl = lane & 7;
-        const bool hi = (lane & 16) != 0, mid = (lane & 8) != 0;
         const int tfinal = tl + 8 * ((hi ? 2 : 0) + (mid ? 1 : 0));  // the tap whose sum this lane ends up with
-        float *wslot = wacc + (size_t)kw * p.C * kSplitWaccPad + tfinal;
+        float *wslot = wacc + (size_t)kw * p.C * WPAD + tfinal;
         for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++tcount) {
             split_wait(table_full, tcount & 1u, abort_flag, p.status, 8);
 
@@ -393,10 +409,83 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
                 if (tfinal < TAPS) {
 #pragma unroll
                     for (int cc = 0; cc < CB; ++cc)
-                        if (g * CB + cc < p.C) wslot[(g * CB + cc) * kSplitWaccPad] += tot[cc];
+                        if (g * CB + cc < p.C) wslot[(g * CB + cc) * WPAD] += tot[cc];
                 }
                 if (++s == (uint32_t)S) s = 0, ph ^= 1u;
             }
+        }
+        } else {
+        // 2D, nine taps: lane = (qw, tl) keeps tap tl (0..7) for its 16 voxels (4 (4 j + qw) + {0..3})
+        // and the ninth tap for two of them - voxel pair tl of the sixteen - as a table that is
+        // zero elsewhere, so both run through the same packed FMAs.  Per channel: the sums of tap
+        // tl meet over the four quarter-warps, those of tap 8 over all 32 lanes (5 shuffles).
+        const int tfinal = lane < 8 ? lane : (lane == 16 ? 8 : TAPS);  // the tap whose sum this lane ends up with
+        float *wslot = wacc + (size_t)kw * p.C * WPAD + (tfinal < TAPS ? tfinal : 0);
+        for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++tcount) {
+            split_wait(table_full, tcount & 1u, abort_flag, p.status, 8);
+
+            float2 Mk[KH / 8], Mk8[KH / 8];  // pairs of neighbouring voxels: operands of packed FMAs
+            {
+                const float4 *m4 = reinterpret_cast<const float4 *>(msm + tl * TS + r * TX + KH * h);
+                const float4 *m8 = reinterpret_cast<const float4 *>(msm + 8 * TS + r * TX + KH * h);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 q = m4[4 * j + qw], q8 = m8[4 * j + qw];
+                    Mk[2 * j] = make_float2(q.x, q.y), Mk[2 * j + 1] = make_float2(q.z, q.w);
+                    Mk8[2 * j] = (tl == 2 * j) ? make_float2(q8.x, q8.y) : make_float2(0.f, 0.f);
+                    Mk8[2 * j + 1] = (tl == 2 * j + 1) ? make_float2(q8.z, q8.w) : make_float2(0.f, 0.f);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) tma::mbar_arrive(m_done);
+
+            for (int g = 0; g < ngroups; ++g) {
+                split_wait(&full[s], ph, abort_flag, p.status, 2);
+                const float4 *ain0 = reinterpret_cast<const float4 *>(ring + s * STAGE + r * TX + KH * h) + qw;  // in[g * CB], this half row
+                float tot[CB];
+#pragma unroll
+                for (int cp = 0; cp < CB; cp += kSplitKU) {
+                    const float4 *ain = ain0 + cp * (CHAN / 4);
+                    float2 acc[kSplitKU], acc8[kSplitKU];
+#pragma unroll
+                    for (int u = 0; u < kSplitKU; ++u) acc[u] = make_float2(0.f, 0.f), acc8[u] = make_float2(0.f, 0.f);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float4 av[kSplitKU];
+#pragma unroll
+                        for (int u = 0; u < kSplitKU; ++u) av[u] = ain[u * (CHAN / 4) + 4 * j];  // one 64-byte run per warp and load
+#pragma unroll
+                        for (int u = 0; u < kSplitKU; ++u) {
+                            const float2 lo = make_float2(av[u].x, av[u].y), up = make_float2(av[u].z, av[u].w);
+                            acc[u] = __ffma2_rn(lo, Mk[2 * j], acc[u]);
+                            acc8[u] = __ffma2_rn(lo, Mk8[2 * j], acc8[u]);
+                            acc[u] = __ffma2_rn(up, Mk[2 * j + 1], acc[u]);
+                            acc8[u] = __ffma2_rn(up, Mk8[2 * j + 1], acc8[u]);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < kSplitKU; ++u) {
+                        const float sa = acc[u].x + acc[u].y, sb = acc8[u].x + acc8[u].y;
+                        // lanes 0-15 end up with tap tl summed over the quarter-warps, lanes 16-31 with tap 8
+                        float v = (hi ? sb : sa) + __shfl_xor_sync(0xffffffffu, hi ? sa : sb, 16);
+                        v += __shfl_xor_sync(0xffffffffu, v, 8);
+                        float w8 = v;  // tap 8 also sums over the eight tap lanes (meaningful in lanes 16-31)
+                        w8 += __shfl_xor_sync(0xffffffffu, w8, 1);
+                        w8 += __shfl_xor_sync(0xffffffffu, w8, 2);
+                        w8 += __shfl_xor_sync(0xffffffffu, w8, 4);
+                        tot[cp + u] = hi ? w8 : v;
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) tma::mbar_arrive(&empty[s]);
+                if (tfinal < TAPS) {
+#pragma unroll
+                    for (int cc = 0; cc < CB; ++cc)
+                        if (g * CB + cc < p.C) wslot[(g * CB + cc) * WPAD] += tot[cc];
+                }
+                if (++s == (uint32_t)S) s = 0, ph ^= 1u;
+            }
+        }
         }
     } else {
         // ===================================== X warps =====================================
@@ -418,7 +507,7 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
                 const float4 q = *reinterpret_cast<const float4 *>(msm + t * TS + r * TX + 4 * xq);
                 M[t][0] = make_float2(q.x, q.y), M[t][1] = make_float2(q.z, q.w);
             }
-            if (valid) bsum += (M[13][0].x + M[13][0].y) + (M[13][1].x + M[13][1].y);  // centre tap = m itself
+            if (valid) bsum += (M[TAPS / 2][0].x + M[TAPS / 2][0].y) + (M[TAPS / 2][1].x + M[TAPS / 2][1].y);  // centre tap = m itself
             __syncwarp();
             if (lane == 0) tma::mbar_arrive(m_done);
 
@@ -435,14 +524,14 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
                     const int c = g * CB + cp;
                     if (c < p.C) {
                         const float4 gq0 = ld4(stage + (CB + cp) * CHAN), gq1 = ld4(stage + (CB + cp + 1) * CHAN);
-                        const float4 *wp0 = reinterpret_cast<const float4 *>(wsm + c * kSplitWPad);
-                        const float4 *wp1 = wp0 + kSplitWPad / 4;
+                        const float4 *wp0 = reinterpret_cast<const float4 *>(wsm + c * WPAD);
+                        const float4 *wp1 = wp0 + WPAD / 4;
                         float gv0[4] = {gq0.x, gq0.y, gq0.z, gq0.w}, gv1[4] = {gq1.x, gq1.y, gq1.z, gq1.w};
                         float4 wa = wp0[0], wb = wp1[0];
 #pragma unroll
-                        for (int i = 0; i < kSplitWPad / 4; ++i) {
+                        for (int i = 0; i < WPAD / 4; ++i) {
                             const float w0[4] = {wa.x, wa.y, wa.z, wa.w}, w1[4] = {wb.x, wb.y, wb.z, wb.w};
-                            if (i + 1 < kSplitWPad / 4) wa = wp0[i + 1], wb = wp1[i + 1];  // the next four taps, ahead of this quad's FMAs
+                            if (i + 1 < WPAD / 4) wa = wp0[i + 1], wb = wp1[i + 1];  // the next four taps, ahead of this quad's FMAs
 #pragma unroll
                             for (int q = 0; q < 4; ++q) {
                                 const int t = 4 * i + q;
@@ -496,7 +585,7 @@ fused_backward3d_split_kernel(const __grid_constant__ CUtensorMap map_in, const 
             const int c = i / TAPS, t = i - c * TAPS;
             float s_ = 0.f;
 #pragma unroll
-            for (int w = 0; w < kSplitKWarps; ++w) s_ += wacc[((size_t)w * p.C + c) * kSplitWaccPad + t];
+            for (int w = 0; w < kSplitKWarps; ++w) s_ += wacc[((size_t)w * p.C + c) * WPAD + t];
             dst[i] = s_;
         }
         if (p.part_b && tid == 0) {

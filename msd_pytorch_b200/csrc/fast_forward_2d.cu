@@ -167,7 +167,7 @@ static const size_t kFwdSmemBudget = 220 * 1024;
 int num_variants(int family) {
     switch (family) {
         case FWD2D: return kNumFwd2dVariants;  // lattice rows x column segments x tile width
-        case BWD2D: return 2;  // 4 / 8 voxels per thread
+        case BWD2D: return 3;  // 4 / 8 voxels per thread / X warps + K warps
         case FWD3D: return kNumFwd3dVariants;  // 4 / 2 column segments per thread / more row stacks
         case BWD3D: return 3;  // unsplit consumers / X warps + K warps / tensor cores
         default: return 1;

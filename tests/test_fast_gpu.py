@@ -281,6 +281,60 @@ def test_role_split_3d_backward_against_cpu_oracle(cuda_device, sp):
         assert_close(w.grad, e, 1e-3, "grad_weight%d" % i)
 
 
+@pytest.mark.parametrize("sp,B", [((37, 128), 3), ((50, 256), 2), ((21, 384), 1)], ids=["x128", "x256", "x384"])
+def test_role_split_2d_backward_against_cpu_oracle(cuda_device, sp, B):
+    """The role-split backward in 2D (launch variant 2 of the 2D backward: X warps, K warps
+    with the ninth tap shared out over the tap lanes, builder warps) directly against the
+    float64 CPU oracle: a depth-24 block with ragged Y, both x borders in one tile (X = 128)
+    and interior tiles (X = 384), every dilation 1..10, channel counts 1..24 (ring stages of
+    four channels that are full, partly filled and single), the number of its launches
+    asserted, and two runs bit-identical."""
+    from oracle import msd_oracle as O
+    from msd_pytorch_b200 import _lib
+    from msd_pytorch_b200.msd_block import block_backward_, block_forward_
+
+    dev = cuda_device
+    L = _lib.lib
+    assert L.msd_tuning_num_variants(_lib.FAMILY_BWD2D) == 3
+    depth = 24
+    dil = [1 + (i % 10) for i in range(depth)]
+    g = torch.Generator().manual_seed(616)
+    x = torch.randn(B, 1, *sp, generator=g)
+    ws = [torch.randn(1, 1 + i, 3, 3, generator=g) * (2.0 / (9 * (1 + i))) ** 0.5 for i in range(depth)]
+    bias = 0.05 * torch.randn(depth, generator=g)
+    gout = torch.randn(B, 1 + depth, *sp, generator=g)
+    res_o = O.msd_block_forward(x.double(), dil, bias.double(), [w.double() for w in ws])
+    gi_o, gb_o, gws_o = O.msd_block_backward(res_o, gout.double(), dil, bias.double(), [w.double() for w in ws])
+    wd = [w.to(dev) for w in ws]
+    res = torch.empty(B, 1 + depth, *sp, device=dev)
+    res[:, :1] = x.to(dev)
+    block_forward_(res, 1, dil, bias.to(dev), wd)
+    assert_close(res, res_o, 1e-4, "activations")
+    old = [L.msd_tuning_get(_lib.FAMILY_BWD2D, d) for d in range(1, 11)]
+    try:
+        for d in range(1, 11):
+            assert L.msd_tuning_set(_lib.FAMILY_BWD2D, d, 2) == 0
+        runs = []
+        for _ in range(2):
+            split0 = L.msd_split_launch_count()
+            g1 = gout.to(dev)
+            gw1 = [torch.zeros_like(w) for w in wd]
+            gb1 = torch.zeros(depth, device=dev)
+            block_backward_(res, g1, 1, dil, wd, gw1, gb1)
+            assert _status(dev) == 0
+            assert L.msd_split_launch_count() - split0 == depth
+            runs.append((g1[:, :1].clone(), gb1, gw1))
+    finally:
+        for d, v in zip(range(1, 11), old):
+            L.msd_tuning_set(_lib.FAMILY_BWD2D, d, v)
+    (gi, gb, gws), (gi2, gb2, gws2) = runs
+    assert torch.equal(gi, gi2) and torch.equal(gb, gb2) and all(torch.equal(a, b) for a, b in zip(gws, gws2))
+    assert_close(gi, gi_o, 1e-3, "grad_input")
+    assert_close(gb, gb_o, 1e-3, "grad_bias")
+    for i, (w, e) in enumerate(zip(gws, gws_o)):
+        assert_close(w, e, 1e-3, "grad_weight%d" % i)
+
+
 def test_bounded_wait_runs_out_and_reports(cuda_device):
     """A wait on a barrier nobody arrives at gives up after its time limit: the kernel returns
     by itself, the device status word carries the code, reading it clears it, and the next
