@@ -49,7 +49,9 @@ struct BwdPlan {
 };
 
 // geometry of the role-split 3D kernel (the constants of the same names there)
-static const int kSplitRows = 4, kSplitKWarps = 8, kSplitCB = 4, kSplitMaxDilation = 12, kSplitMaxStages = 8, kSplitHeader = 512;
+static const int kSplitKWarps = 8, kSplitMaxDilation = 12, kSplitMaxStages = 8, kSplitHeader = 512;
+static int split_rows(int nd) { return nd == 3 ? 4 : 8; }  // rows per tile
+static int split_cb(int nd) { return nd == 3 ? 4 : 2; }    // channels per ring stage
 // below this many input channels the per-tile set-up of the split kernel outweighs its faster
 // channel loop (large dilations have more border tiles, whose set-up reads global memory)
 static int split_min_channels(int d) { return d <= 5 ? 8 : 10; }
@@ -81,12 +83,12 @@ static bool plan(const BackwardArgs &a, BwdPlan *pl) {
     const bool split3d = nd == 3 && C >= split_min_channels(a.d) && tuning_get(BWD3D, a.d) != 0;
     const bool split2d = nd == 2 && tuning_get(BWD2D, a.d) == 2;
     if ((split3d || split2d) && do_x && do_k && (g.x % 128) == 0 && a.d <= kSplitMaxDilation) {
-        // role-split kernel: 4 X warps + 8 K warps on tiles of 4 rows x 128 columns, kSplitCB
-        // channels per ring stage; the table of M (27 or 9 taps x (4 x 128 + 4) floats) beside the (double-buffered) halo rows
-        const int TR = kSplitRows, TXP = 128 + 2 * Dp;
+        // role-split kernel: 4 X warps + 8 K warps on tiles of 4 (2D: 8) rows x 128 columns, 4 (2)
+        // channels per ring stage; the table of M (27 or 9 taps x (rows x 128 + 4) floats) beside the (double-buffered) halo rows
+        const int TR = split_rows(nd), TXP = 128 + 2 * Dp;
         const size_t halo = 2 * (size_t)RT * ((TR * TXP + 31) & ~31) * (a.out ? 2 : 1) + ((3 * RT * (TR * 128 + 4) + 31) & ~31);  // two halo buffers + the table
         const size_t fixed = kSplitHeader + (size_t)4 * (C * TAPS_PAD + (size_t)kSplitKWarps * C * TAPS_PAD + halo);
-        const size_t stage = (size_t)4 * 2 * kSplitCB * TR * 128;
+        const size_t stage = (size_t)4 * 2 * split_cb(nd) * TR * 128;
         if (fixed + 2 * stage <= kSmemBudget) {
             int s = (int)((kSmemBudget - fixed) / stage);
             if (s > kSplitMaxStages) s = kSplitMaxStages;
@@ -264,7 +266,7 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
     p.N = (int)g.n, p.C = (int)C, p.Z = (int)g.z, p.Y = (int)g.y, p.X = (int)g.x;
     p.d = a.d, p.Dp = (a.d + 3) & ~3;
     const int TX = pl.txq16 ? 64 : 128;
-    const int TR = pl.mma ? kMmaRowsHost : pl.split ? kSplitRows : (bwd_consumer_warps(a.nd) * 32 / (TX / 4)) * pl.j;
+    const int TR = pl.mma ? kMmaRowsHost : pl.split ? split_rows(a.nd) : (bwd_consumer_warps(a.nd) * 32 / (TX / 4)) * pl.j;
     get_z_window((int)g.z, &p.z0, &p.ZW);
     p.tiles_x = (int)ceil_div(g.x, TX);
     p.tiles_y = (int)ceil_div(g.y, TR);
@@ -306,7 +308,7 @@ int backward(const BackwardArgs &a, int device, cudaStream_t s) {
                 if (rc2) return rc2;
                 continue;
             }
-            const int cbox = (which < 2) ? (pl.split ? kSplitCB : pl.mma ? kMmaCBHost : 1) : 1;  // channels per box
+            const int cbox = (which < 2) ? (pl.split ? split_cb(a.nd) : pl.mma ? kMmaCBHost : 1) : 1;  // channels per box
             int box[5] = {which < 2 ? TX : TX + 2 * p.Dp, TR, a.nd == 3 ? 1 : cbox, a.nd == 3 ? cbox : 1, 1};
             int64_t dims[5], strides[5];
             if (a.nd == 3) {

@@ -10,21 +10,22 @@
 //            shared loads and accumulates  sum_v in[c][v] * M_t[v]  with packed FMAs; the
 //            four quarter-warps' sums meet in a 3-shuffle reduce-scatter (the full shuffle
 //            tree of the unsplit kernel costs 124 instructions per 216 FMAs in 3D).
-//            2D: the same lanes; a lane keeps tap `tap lane` (0..7) for its 16 voxels and the
-//            ninth tap for two of them (the eight tap lanes of a quarter-warp share it out);
-//            five shuffles per channel.
+//            2D: a lane keeps tap `tap lane` (0..7) for the 32 voxels of its quarter of a tile
+//            row and the ninth tap for four of them (the eight tap lanes of a quarter-warp share
+//            it out); five shuffles per channel.
 //
-// A tile is 4 rows x 128 columns of one z-plane (image).  The block has four warpgroups:
-//   warps 0-3    X warps, one per tile row               (registers raised to kSplitRegsX)
-//   warps 4-11   K warps, (row, half) = (w-4)/2, (w-4)%2 (the launch's 128 registers)
+// A tile is 4 rows x 128 columns of one z-plane (3D) or 8 rows x 128 columns (2D).  The block
+// has four warpgroups:
+//   warps 0-3    X warps, one per tile row (2D: rows w and w + 4)   (registers raised to kSplitRegsX)
+//   warps 4-11   K warps, 3D: (row, half) = (w-4)/2, (w-4)%2; 2D: row w-4  (the launch's 128 registers)
 //   warp 12      TMA producer                            (registers lowered to kSplitRegsP)
 //   warps 13-15  builders of the table of M (below)      (same warpgroup as the producer)
 // so that each of the four warp schedulers (warp id mod 4) carries one X warp and two K warps.
 // The register file is re-divided between the warpgroups with setmaxnreg: the 3D X warps need
 // 108 registers for M alone, the producer and the builders few.
 //
-// Data movement.  One ring stage holds kSplitCB consecutive channels of the tile: two TMA
-// boxes (activations, gradients) of kSplitCB x 4 x 128 floats, so that the cost of issuing a
+// Data movement.  One ring stage holds 4 (2D: 2) consecutive channels of the tile: two TMA
+// boxes (activations, gradients) of 4 x 4 x 128 (2 x 8 x 128) floats, so that the cost of issuing a
 // copy and of the full/empty hand-shake is paid once per kSplitCB channels.  The 9 (3) halo row
 // groups of gout (and of out, for the ReLU gate) land by TMA in one of two buffers (tiles
 // alternate), requested a whole tile ahead.  The builder warps turn them into
@@ -44,13 +45,15 @@
 namespace msd {
 namespace fast {
 
-constexpr int kSplitRows = 4;
+constexpr int kSplitRows = 4;                                     // 3D: rows per tile
+constexpr int split_rows(int nd) { return nd == 3 ? kSplitRows : 8; }  // 2D: 8 rows (two per X warp, one per K warp)
 constexpr int kSplitTX = 128;
-constexpr int kSplitCB = 4;                                       // channels per ring stage
+constexpr int kSplitCB = 4;                                       // 3D: channels per ring stage
+constexpr int split_cb(int nd) { return nd == 3 ? kSplitCB : 2; }  // 2D: two (a stage is 2 tensors x 2 channels x 8 rows x 128)
 constexpr int kSplitKU = 2;                                       // channels a K warp processes per loop iteration (4: measured 4 % slower)
-constexpr int kSplitKHalf = 64;                                   // voxels per K warp
-constexpr int kSplitXWarps = kSplitRows;
-constexpr int kSplitKWarps = 2 * kSplitRows;
+constexpr int kSplitKHalf = 64;                                   // 3D: voxels per K warp (half a row); 2D: a whole row
+constexpr int kSplitXWarps = 4;
+constexpr int kSplitKWarps = 8;
 constexpr int kSplitConsumerWarps = kSplitXWarps + kSplitKWarps;  // 12
 constexpr int kSplitConsumers = kSplitConsumerWarps * 32;         // 384
 constexpr int kSplitThreads = 512;                                // four warpgroups
@@ -139,9 +142,9 @@ __device__ __forceinline__ float4 split_shift4(const float4 &a, const float4 &b)
 // The builder warps share their schedulers with three consumer warps each, so what counts is
 // how few instructions a row takes (a version with one scalar load and store per float was
 // 2 - 4 % slower on layers of 25 and more channels).
-template <int SH, int RT>
+template <int SH, int RT, int TR>
 __device__ __forceinline__ void split_build_table_sh(const BwdParams &p, const float *rows, float *msm, int HSLOT, int TXP, int TS, int btid, int x0) {
-    constexpr int TR = kSplitRows, TX = kSplitTX;
+    constexpr int TX = kSplitTX;
     const bool fold_l = x0 == 0, fold_r = x0 + TX == p.X;
     const int lane = btid & 31, qd = p.d >> 2;
     const bool lane_l = fold_l && 4 * lane < p.d, lane_r = fold_r && 4 * lane + 3 >= TX - p.d;
@@ -173,13 +176,13 @@ __device__ __forceinline__ void split_build_table_sh(const BwdParams &p, const f
     }
 }
 
-template <int RT>
+template <int RT, int TR>
 __device__ __forceinline__ void split_build_table(const BwdParams &p, const float *rows, float *msm, int HSLOT, int TXP, int TS, int btid, int x0) {
     switch (p.d & 3) {
-        case 0: split_build_table_sh<0, RT>(p, rows, msm, HSLOT, TXP, TS, btid, x0); break;
-        case 1: split_build_table_sh<1, RT>(p, rows, msm, HSLOT, TXP, TS, btid, x0); break;
-        case 2: split_build_table_sh<2, RT>(p, rows, msm, HSLOT, TXP, TS, btid, x0); break;
-        default: split_build_table_sh<3, RT>(p, rows, msm, HSLOT, TXP, TS, btid, x0); break;
+        case 0: split_build_table_sh<0, RT, TR>(p, rows, msm, HSLOT, TXP, TS, btid, x0); break;
+        case 1: split_build_table_sh<1, RT, TR>(p, rows, msm, HSLOT, TXP, TS, btid, x0); break;
+        case 2: split_build_table_sh<2, RT, TR>(p, rows, msm, HSLOT, TXP, TS, btid, x0); break;
+        default: split_build_table_sh<3, RT, TR>(p, rows, msm, HSLOT, TXP, TS, btid, x0); break;
     }
 }
 
@@ -198,7 +201,8 @@ __global__ void __launch_bounds__(kSplitThreads, 1)
 fused_backward_split_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_gin,
                             const __grid_constant__ CUtensorMap map_gout, const __grid_constant__ CUtensorMap map_out, const BwdParams p) {
     constexpr int RT = ND == 3 ? 9 : 3, TAPS = 3 * RT, WPAD = split_taps_pad(ND);
-    constexpr int TX = kSplitTX, TR = kSplitRows, KH = kSplitKHalf, CB = kSplitCB;
+    constexpr int TX = kSplitTX, TR = split_rows(ND), KH = kSplitKHalf, CB = split_cb(ND);
+    constexpr int XR = TR / kSplitXWarps;  // rows per X warp
     constexpr int CHAN = TR * TX;        // floats of one channel of one tensor in a stage
     constexpr int STAGE = 2 * CB * CHAN;  // CB channels of in, then CB channels of gin
 
@@ -314,10 +318,10 @@ fused_backward_split_kernel(const __grid_constant__ CUtensorMap map_in, const __
                 const int hb = tcount & 1;
                 float *rows = rows0 + hb * HBUF, *orows = rows + RT * HSLOT;
                 split_wait(&halo_full[hb], (tcount >> 1) & 1u, abort_flag, p.status, 6);
-                split_fill_rows<kSplitBuilders, kSplitRows, ND>(p, rows, orows, HSLOT, TXP, gate, btid, n, z, y0, x0);
+                split_fill_rows<kSplitBuilders, TR, ND>(p, rows, orows, HSLOT, TXP, gate, btid, n, z, y0, x0);
                 if (tcount) split_wait(m_done, (tcount - 1) & 1u, abort_flag, p.status, 7);  // the previous table has been read
                 tma::named_barrier(3, kSplitBuilders);
-                split_build_table<RT>(p, rows, msm, HSLOT, TXP, TS, btid, x0);
+                split_build_table<RT, TR>(p, rows, msm, HSLOT, TXP, TS, btid, x0);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the reads of the rows, before TMA rewrites them
                 tma::named_barrier(3, kSplitBuilders);
                 if (btid == 0) {
@@ -332,10 +336,11 @@ fused_backward_split_kernel(const __grid_constant__ CUtensorMap map_in, const __
     uint32_t tcount = 0, s = 0, ph = 0;
     if (warp >= kSplitXWarps) {
         // ===================================== K warps =====================================
-        const int kw = warp - kSplitXWarps, r = kw >> 1, h = kw & 1;
+        const int kw = warp - kSplitXWarps;
         const int qw = lane >> 3, tl = lane & 7;
         const bool hi = (lane & 16) != 0, mid = (lane & 8) != 0;
         if constexpr (ND == 3) {
+        const int r = kw >> 1, h = kw & 1;
         // lane = (qw, tl): taps tl + 8 {0..3}; voxels 4 (4 j + qw) + {0..3}, j = 0..3, of the half row.
         // The four quarter-warps read four neighbouring 16-byte pieces of the activations per
         // load; the eight lanes of a quarter-warp (one phase of a 128-bit shared load) read
@@ -415,57 +420,63 @@ fused_backward_split_kernel(const __grid_constant__ CUtensorMap map_in, const __
             }
         }
         } else {
-        // 2D, nine taps: lane = (qw, tl) keeps tap tl (0..7) for its 16 voxels (4 (4 j + qw) + {0..3})
-        // and the ninth tap for two of them - voxel pair tl of the sixteen - as a table that is
-        // zero elsewhere, so both run through the same packed FMAs.  Per channel: the sums of tap
-        // tl meet over the four quarter-warps, those of tap 8 over all 32 lanes (5 shuffles).
+        // 2D, nine taps, one K warp per tile row: lane = (qw, tl) keeps tap tl (0..7) for the 32
+        // voxels 32 qw + {0..31} of its row and the ninth tap for four of them (the 16-byte piece
+        // tl of those 32 voxels), which costs one more 128-bit load (conflict-free: the eight
+        // lanes of a phase read 128 consecutive bytes) and two more packed FMAs per channel.
+        // Per channel: the sums of tap tl meet over the four quarter-warps, those of tap 8 over
+        // all 32 lanes (5 shuffles).
+        const int r = kw;
+        (void)mid;
         const int tfinal = lane < 8 ? lane : (lane == 16 ? 8 : TAPS);  // the tap whose sum this lane ends up with
         float *wslot = wacc + (size_t)kw * p.C * WPAD + (tfinal < TAPS ? tfinal : 0);
         for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++tcount) {
             split_wait(table_full, tcount & 1u, abort_flag, p.status, 8);
 
-            float2 Mk[KH / 8], Mk8[KH / 8];  // pairs of neighbouring voxels: operands of packed FMAs
+            float2 Mk[16], Mk8[2];  // pairs of neighbouring voxels: operands of packed FMAs
             {
-                const float4 *m4 = reinterpret_cast<const float4 *>(msm + tl * TS + r * TX + KH * h);
-                const float4 *m8 = reinterpret_cast<const float4 *>(msm + 8 * TS + r * TX + KH * h);
+                const float4 *m4 = reinterpret_cast<const float4 *>(msm + tl * TS + r * TX) + 8 * qw;
+                const float4 *m8 = reinterpret_cast<const float4 *>(msm + 8 * TS + r * TX) + 8 * qw;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float4 q = m4[4 * j + qw], q8 = m8[4 * j + qw];
+                for (int j = 0; j < 8; ++j) {
+                    const float4 q = m4[j];
                     Mk[2 * j] = make_float2(q.x, q.y), Mk[2 * j + 1] = make_float2(q.z, q.w);
-                    Mk8[2 * j] = (tl == 2 * j) ? make_float2(q8.x, q8.y) : make_float2(0.f, 0.f);
-                    Mk8[2 * j + 1] = (tl == 2 * j + 1) ? make_float2(q8.z, q8.w) : make_float2(0.f, 0.f);
                 }
+                const float4 q8 = m8[tl];
+                Mk8[0] = make_float2(q8.x, q8.y), Mk8[1] = make_float2(q8.z, q8.w);
             }
             __syncwarp();
             if (lane == 0) tma::mbar_arrive(m_done);
 
             for (int g = 0; g < ngroups; ++g) {
                 split_wait(&full[s], ph, abort_flag, p.status, 2);
-                const float4 *ain0 = reinterpret_cast<const float4 *>(ring + s * STAGE + r * TX + KH * h) + qw;  // in[g * CB], this half row
+                const float4 *ain0 = reinterpret_cast<const float4 *>(ring + s * STAGE + r * TX) + 8 * qw;  // in[g * CB], this row, this quarter
                 float tot[CB];
 #pragma unroll
                 for (int cp = 0; cp < CB; cp += kSplitKU) {
                     const float4 *ain = ain0 + cp * (CHAN / 4);
-                    float2 acc[kSplitKU], acc8[kSplitKU];
+                    float2 acc[kSplitKU][2], acc8[kSplitKU];
 #pragma unroll
-                    for (int u = 0; u < kSplitKU; ++u) acc[u] = make_float2(0.f, 0.f), acc8[u] = make_float2(0.f, 0.f);
+                    for (int u = 0; u < kSplitKU; ++u) {
+                        const float4 a8 = ain[u * (CHAN / 4) + tl];
+                        acc[u][0] = make_float2(0.f, 0.f), acc[u][1] = make_float2(0.f, 0.f);
+                        acc8[u] = __ffma2_rn(make_float2(a8.x, a8.y), Mk8[0], make_float2(0.f, 0.f));
+                        acc8[u] = __ffma2_rn(make_float2(a8.z, a8.w), Mk8[1], acc8[u]);
+                    }
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
+                    for (int j = 0; j < 8; ++j) {
                         float4 av[kSplitKU];
 #pragma unroll
-                        for (int u = 0; u < kSplitKU; ++u) av[u] = ain[u * (CHAN / 4) + 4 * j];  // one 64-byte run per warp and load
+                        for (int u = 0; u < kSplitKU; ++u) av[u] = ain[u * (CHAN / 4) + j];  // one 16-byte piece per quarter-warp
 #pragma unroll
                         for (int u = 0; u < kSplitKU; ++u) {
-                            const float2 lo = make_float2(av[u].x, av[u].y), up = make_float2(av[u].z, av[u].w);
-                            acc[u] = __ffma2_rn(lo, Mk[2 * j], acc[u]);
-                            acc8[u] = __ffma2_rn(lo, Mk8[2 * j], acc8[u]);
-                            acc[u] = __ffma2_rn(up, Mk[2 * j + 1], acc[u]);
-                            acc8[u] = __ffma2_rn(up, Mk8[2 * j + 1], acc8[u]);
+                            acc[u][0] = __ffma2_rn(make_float2(av[u].x, av[u].y), Mk[2 * j], acc[u][0]);
+                            acc[u][1] = __ffma2_rn(make_float2(av[u].z, av[u].w), Mk[2 * j + 1], acc[u][1]);
                         }
                     }
 #pragma unroll
                     for (int u = 0; u < kSplitKU; ++u) {
-                        const float sa = acc[u].x + acc[u].y, sb = acc8[u].x + acc8[u].y;
+                        const float sa = (acc[u][0].x + acc[u][0].y) + (acc[u][1].x + acc[u][1].y), sb = acc8[u].x + acc8[u].y;
                         // lanes 0-15 end up with tap tl summed over the quarter-warps, lanes 16-31 with tap 8
                         float v = (hi ? sb : sa) + __shfl_xor_sync(0xffffffffu, hi ? sa : sb, 16);
                         v += __shfl_xor_sync(0xffffffffu, v, 8);
@@ -500,14 +511,19 @@ fused_backward_split_kernel(const __grid_constant__ CUtensorMap map_in, const __
             const int x0 = tx_i * TX, y0 = ty_i * TR;
             split_wait(table_full, tcount & 1u, abort_flag, p.status, 8);
 
-            float2 M[TAPS][2];  // pairs of neighbouring voxels: operands of packed FMAs
-            const bool valid = (y0 + r) < p.Y;
+            // XR rows per warp (r, r + 4, ...), each with four voxels per lane
+            float2 M[XR][TAPS][2];  // pairs of neighbouring voxels
+            bool valid[XR];
 #pragma unroll
-            for (int t = 0; t < TAPS; ++t) {
-                const float4 q = *reinterpret_cast<const float4 *>(msm + t * TS + r * TX + 4 * xq);
-                M[t][0] = make_float2(q.x, q.y), M[t][1] = make_float2(q.z, q.w);
+            for (int xr = 0; xr < XR; ++xr) {
+                valid[xr] = (y0 + r + 4 * xr) < p.Y;
+#pragma unroll
+                for (int t = 0; t < TAPS; ++t) {
+                    const float4 q = *reinterpret_cast<const float4 *>(msm + t * TS + (r + 4 * xr) * TX + 4 * xq);
+                    M[xr][t][0] = make_float2(q.x, q.y), M[xr][t][1] = make_float2(q.z, q.w);
+                }
+                if (valid[xr]) bsum += (M[xr][TAPS / 2][0].x + M[xr][TAPS / 2][0].y) + (M[xr][TAPS / 2][1].x + M[xr][TAPS / 2][1].y);  // centre tap = m itself
             }
-            if (valid) bsum += (M[TAPS / 2][0].x + M[TAPS / 2][0].y) + (M[TAPS / 2][1].x + M[TAPS / 2][1].y);  // centre tap = m itself
             __syncwarp();
             if (lane == 0) tma::mbar_arrive(m_done);
 
@@ -515,18 +531,23 @@ fused_backward_split_kernel(const __grid_constant__ CUtensorMap map_in, const __
             for (int g = 0; g < ngroups; ++g) {
                 split_wait(&full[s], ph, abort_flag, p.status, 2);
                 const float *stage = ring + s * STAGE + r * TX + 4 * xq;
-                const bool live = valid && !*abort_flag;
-                // two channels at a time: eight independent FMA chains that share the M operands.
+                const bool live = !*abort_flag;
+                // two channels at a time: 8 XR independent FMA chains that share the M operands.
                 // When C is odd the last pair's second channel reads a zero-filled stage and
                 // whatever follows the weights in shared memory; its result is not stored.
 #pragma unroll
                 for (int cp = 0; cp < CB; cp += 2) {
                     const int c = g * CB + cp;
                     if (c < p.C) {
-                        const float4 gq0 = ld4(stage + (CB + cp) * CHAN), gq1 = ld4(stage + (CB + cp + 1) * CHAN);
                         const float4 *wp0 = reinterpret_cast<const float4 *>(wsm + c * WPAD);
                         const float4 *wp1 = wp0 + WPAD / 4;
-                        float gv0[4] = {gq0.x, gq0.y, gq0.z, gq0.w}, gv1[4] = {gq1.x, gq1.y, gq1.z, gq1.w};
+                        float gv0[XR][4], gv1[XR][4];
+#pragma unroll
+                        for (int xr = 0; xr < XR; ++xr) {
+                            const float4 gq0 = ld4(stage + (CB + cp) * CHAN + 4 * xr * TX), gq1 = ld4(stage + (CB + cp + 1) * CHAN + 4 * xr * TX);
+                            gv0[xr][0] = gq0.x, gv0[xr][1] = gq0.y, gv0[xr][2] = gq0.z, gv0[xr][3] = gq0.w;
+                            gv1[xr][0] = gq1.x, gv1[xr][1] = gq1.y, gv1[xr][2] = gq1.z, gv1[xr][3] = gq1.w;
+                        }
                         float4 wa = wp0[0], wb = wp1[0];
 #pragma unroll
                         for (int i = 0; i < WPAD / 4; ++i) {
@@ -536,32 +557,39 @@ fused_backward_split_kernel(const __grid_constant__ CUtensorMap map_in, const __
                             for (int q = 0; q < 4; ++q) {
                                 const int t = 4 * i + q;
                                 if (t < TAPS) {
-                                    gv0[0] = fmaf(w0[q], M[t][0].x, gv0[0]), gv1[0] = fmaf(w1[q], M[t][0].x, gv1[0]);
-                                    gv0[1] = fmaf(w0[q], M[t][0].y, gv0[1]), gv1[1] = fmaf(w1[q], M[t][0].y, gv1[1]);
-                                    gv0[2] = fmaf(w0[q], M[t][1].x, gv0[2]), gv1[2] = fmaf(w1[q], M[t][1].x, gv1[2]);
-                                    gv0[3] = fmaf(w0[q], M[t][1].y, gv0[3]), gv1[3] = fmaf(w1[q], M[t][1].y, gv1[3]);
+#pragma unroll
+                                    for (int xr = 0; xr < XR; ++xr) {
+                                        gv0[xr][0] = fmaf(w0[q], M[xr][t][0].x, gv0[xr][0]), gv1[xr][0] = fmaf(w1[q], M[xr][t][0].x, gv1[xr][0]);
+                                        gv0[xr][1] = fmaf(w0[q], M[xr][t][0].y, gv0[xr][1]), gv1[xr][1] = fmaf(w1[q], M[xr][t][0].y, gv1[xr][1]);
+                                        gv0[xr][2] = fmaf(w0[q], M[xr][t][1].x, gv0[xr][2]), gv1[xr][2] = fmaf(w1[q], M[xr][t][1].x, gv1[xr][2]);
+                                        gv0[xr][3] = fmaf(w0[q], M[xr][t][1].y, gv0[xr][3]), gv1[xr][3] = fmaf(w1[q], M[xr][t][1].y, gv1[xr][3]);
+                                    }
                                 }
                             }
                         }
-                        // a channel that is the output of the layer below: hand its gradient over
-                        // already multiplied by that layer's ReLU gate
-                        if (c == p.mask_channel) {
-                            const float4 a = ld4(stage + cp * CHAN);
-                            gv0[0] = a.x > 0.f ? gv0[0] : 0.f;
-                            gv0[1] = a.y > 0.f ? gv0[1] : 0.f;
-                            gv0[2] = a.z > 0.f ? gv0[2] : 0.f;
-                            gv0[3] = a.w > 0.f ? gv0[3] : 0.f;
-                        }
-                        if (c + 1 == p.mask_channel) {
-                            const float4 a = ld4(stage + (cp + 1) * CHAN);
-                            gv1[0] = a.x > 0.f ? gv1[0] : 0.f;
-                            gv1[1] = a.y > 0.f ? gv1[1] : 0.f;
-                            gv1[2] = a.z > 0.f ? gv1[2] : 0.f;
-                            gv1[3] = a.w > 0.f ? gv1[3] : 0.f;
-                        }
-                        if (live) {
-                            *reinterpret_cast<float4 *>(gi_row + c * p.gi_sc) = make_float4(gv0[0], gv0[1], gv0[2], gv0[3]);
-                            if (c + 1 < p.C) *reinterpret_cast<float4 *>(gi_row + (c + 1) * p.gi_sc) = make_float4(gv1[0], gv1[1], gv1[2], gv1[3]);
+#pragma unroll
+                        for (int xr = 0; xr < XR; ++xr) {
+                            // a channel that is the output of the layer below: hand its gradient over
+                            // already multiplied by that layer's ReLU gate
+                            if (c == p.mask_channel) {
+                                const float4 a = ld4(stage + cp * CHAN + 4 * xr * TX);
+                                gv0[xr][0] = a.x > 0.f ? gv0[xr][0] : 0.f;
+                                gv0[xr][1] = a.y > 0.f ? gv0[xr][1] : 0.f;
+                                gv0[xr][2] = a.z > 0.f ? gv0[xr][2] : 0.f;
+                                gv0[xr][3] = a.w > 0.f ? gv0[xr][3] : 0.f;
+                            }
+                            if (c + 1 == p.mask_channel) {
+                                const float4 a = ld4(stage + (cp + 1) * CHAN + 4 * xr * TX);
+                                gv1[xr][0] = a.x > 0.f ? gv1[xr][0] : 0.f;
+                                gv1[xr][1] = a.y > 0.f ? gv1[xr][1] : 0.f;
+                                gv1[xr][2] = a.z > 0.f ? gv1[xr][2] : 0.f;
+                                gv1[xr][3] = a.w > 0.f ? gv1[xr][3] : 0.f;
+                            }
+                            if (live && valid[xr]) {
+                                float *dst = gi_row + (int64_t)(4 * xr) * p.gi_sy;
+                                *reinterpret_cast<float4 *>(dst + c * p.gi_sc) = make_float4(gv0[xr][0], gv0[xr][1], gv0[xr][2], gv0[xr][3]);
+                                if (c + 1 < p.C) *reinterpret_cast<float4 *>(dst + (c + 1) * p.gi_sc) = make_float4(gv1[xr][0], gv1[xr][1], gv1[xr][2], gv1[xr][3]);
+                            }
                         }
                     }
                 }
