@@ -244,7 +244,11 @@ MSD_API int msd_slab_layer_backward(const msd_tensor_t *result, const msd_tensor
  * channels whose x extent is a multiple of 128; variant 2 = the input gradient as a
  * TF32 tensor-core contraction with error-compensated operand splitting (tcgen05,
  * float32-level accuracy), the weight gradient on the CUDA cores (8 to ~88 input
- * channels, x extent a multiple of 128, already gated gradient). */
+ * channels, x extent a multiple of 128, already gated gradient).
+ * 2D backward: variant 0 / 1 (default) = 4 / 8 voxels per thread, one kind of consumer
+ * warp; variant 2 = warps split by role as in 3D (x extent a multiple of 128).
+ * Forward: tile shapes (rows of the row lattice, column segments per thread, tile
+ * width); an untuned 2D forward uses the shapes that won on a large image. */
 MSD_API int msd_tuning_num_variants(int family);
 
 /* Force variant `variant` (or -1 = library default) for (family, dilation).
