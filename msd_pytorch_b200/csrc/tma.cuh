@@ -20,7 +20,8 @@ namespace tma {
 int *device_status_ptr(int device);  // host; nullptr on failure
 
 constexpr uint64_t kWaitLimitNs = 4000000000ull;  // 4 s: far beyond any legitimate wait (a layer's kernel runs for milliseconds)
-constexpr uint64_t kAbortWaitLimitNs = 200000ull;  // once a time-out happened in the block, later waits give up after 0.2 ms
+constexpr uint64_t kAbortWaitLimitNs = 200000ull;  // once a time-out happened in the block, later waits give up after 0.2 ms (plus one batch of polls)
+constexpr uint32_t kParkNs = 5000u;  // longest time one poll of a wait may stay parked by the hardware
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
@@ -61,6 +62,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     return ok != 0;
 }
 
+// try_wait with a suspend-time hint: the hardware may park the thread for up to `hint_ns`
+// nanoseconds, or until the phase completes, instead of returning at once.  A waiting warp (the
+// producer between two ring stages, consumers waiting for data) then does not take issue slots
+// from the warps it waits for; measured 1 - 2 % on the backward kernels.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t *bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+
 // Bounded wait for the phase with the given parity.  `abort_flag` is a shared-memory word
 // of the block: once any thread's wait ran out, all later waits in the block use the short
 // limit, the block keeps its control flow (so every barrier is still reached) and skips its
@@ -70,13 +87,13 @@ __device__ __forceinline__ void wait_parity(uint64_t *bar, uint32_t parity, vola
                                             uint64_t limit_ns = kWaitLimitNs) {
 #pragma unroll 1
     for (int i = 0; i < 16; ++i)
-        if (mbar_try_wait(bar, parity)) return;
+        if (mbar_try_wait_parked(bar, parity, kParkNs)) return;
     const uint64_t t0 = globaltimer_ns();
 #pragma unroll 1
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 32; ++i)
-            if (mbar_try_wait(bar, parity)) return;
+            if (mbar_try_wait_parked(bar, parity, kParkNs)) return;
         const uint64_t limit = *abort_flag ? kAbortWaitLimitNs : limit_ns;
         if (globaltimer_ns() - t0 > limit) break;
     }
